@@ -1,0 +1,72 @@
+// tma_host.cuh -- host-side construction of TMA tensor maps without linking libcuda: the
+// driver's cuTensorMapEncodeTiled is looked up through the runtime.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fluke_sm100 {
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline encode_tiled_fn get_encode_tiled() {
+    static encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_tiled_fn>(p);
+    }
+    return fn;
+}
+
+// Row-major 2-D tensor [rows, cols] with `row_stride_bytes` between rows (multiple of 16),
+// copied in boxes of box_rows x box_cols elements; box_cols * elem_bytes must be 128 when the
+// 128-byte swizzle is used. Out-of-range parts of a box read as zero and are not written.
+inline int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, uint32_t elem_bytes,
+                        const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                        uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+    encode_tiled_fn fn = get_encode_tiled();
+    if (!fn) return (int)cudaErrorNotSupported;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (row_stride_bytes & 15u))
+        return (int)cudaErrorMisalignedAddress;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    CUresult r = fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+// Row-major 3-D tensor [planes, rows, cols]; boxes are 1 x box_rows x box_cols.
+inline int make_tmap_3d(CUtensorMap *m, CUtensorMapDataType dt, const void *base, uint64_t planes,
+                        uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                        uint64_t plane_stride_bytes, uint32_t box_rows, uint32_t box_cols,
+                        bool swizzle128) {
+    encode_tiled_fn fn = get_encode_tiled();
+    if (!fn) return (int)cudaErrorNotSupported;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (row_stride_bytes & 15u) ||
+        (plane_stride_bytes & 15u))
+        return (int)cudaErrorMisalignedAddress;
+    cuuint64_t dims[3] = {cols, rows, planes};
+    cuuint64_t strides[2] = {row_stride_bytes, plane_stride_bytes};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, dt, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace fluke_sm100
