@@ -1,0 +1,387 @@
+"""Benchmark of the factored-LSTM basecaller stack on B200 (sm_100a), one JSON line.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the headline metric is quoted on): 5 factored-LSTM layers of
+alternating direction, hidden 768, factor rank 128, T = 1000 timesteps, 1024 chunks PER GPU
+(weak scaling: chunks are independent, every rank runs its own batch, no collective on the data
+path). One "step" = one pass of the whole stack over one [T, B, 768] int8 batch.
+
+    value            chunk-timesteps per second per layer, summed over GPUs
+                     = n_gpus * B * T * layers / step_time   (inputs resident in HBM)
+    e2e              the same through the public API with HOST buffers: pinned-host -> device
+                     copy of the step's input and device -> host copy of its output inside
+                     the timed region
+    roofline         the fused LSTM step kernel (tensor bound): algorithmic FLOPs per launch /
+                     its average launch duration, measured with CUDA events on the launching
+                     stream, against the measured bf16 GEMM peak of this pool
+    cpu_baseline     the CPU oracle (oracle/fluke_oracle.c, a port: the reference has no CPU
+                     implementation of the LSTM contraction) on a bounded sample, all host cores
+    ops              the other configurations of the path (rotary, RMSNorm(+quant), QKV GEMM +
+                     rotary, dual GEMM + SiLU) timed with rotating buffers larger than L2
+
+`--impl reference` times the CPU oracle of the same workload on the host cores (bounded sample
+per step) and prints the same line with "impl": "reference".
+Synthetic seeded data throughout (weights N(0, 1/sqrt(fan_in)), inputs N(0,1)).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+T_STEPS, HIDDEN, RANK, LAYERS, CHUNKS_PER_GPU = 1000, 768, 128, 5, 1024
+METRIC = "lstm_chunk_timesteps_per_sec_per_layer"
+UNIT = "chunk-timesteps/s (per layer, summed over GPUs)"
+
+
+# ---- helpers shared with the CPU tests -----------------------------------------------------------
+
+def local_units(chunks, timesteps, layers):
+    """Work units one rank processes per step (chunk-timesteps x layers)."""
+    return chunks * timesteps * layers
+
+
+def reduce_step_time(ms):
+    """Max over ranks of a per-rank step time (identity without torch.distributed)."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        return ms
+    dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        self.thread.join(2)
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 9 for i in range(4) if r[5 + i].lower() == "active"})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---- CPU arm (oracle port) -------------------------------------------------------------------------
+
+def cpu_lstm_sample(seconds_target=15.0):
+    """Times the CPU oracle on a bounded sample of the workload (1 layer, B chunks, T steps of
+    the same shapes); returns (chunk-timesteps/s per layer, cores, description)."""
+    import torch
+    from fluke_b200 import prep
+    from oracle import port
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    g = torch.Generator().manual_seed(42)
+    H, R = HIDDEN, RANK
+
+    def run(B, T):
+        dn_ih, s_ih = prep.quantize_int8_rows(torch.randn(R, H, generator=g) / H ** 0.5)
+        dn_hh, s_hh = prep.quantize_int8_rows(torch.randn(R, H, generator=g) / H ** 0.5)
+        w_up = (torch.randn(4 * H, 2 * R, generator=g) / (2 * R) ** 0.5).half()
+        bias = torch.randn(4 * H, generator=g) * 0.05
+        x, xs = prep.quantize_int8_rows(torch.randn(T * B, H, generator=g))
+        t0 = time.perf_counter()
+        port.lstm_layer(x.view(T, B, H).numpy(), xs.numpy(), dn_ih.numpy(), s_ih.numpy(), dn_hh.numpy(), s_hh.numpy(),
+                        w_up.numpy(), bias.numpy(), np.zeros((B, H), np.float32), np.zeros((B, H), np.int8))
+        return time.perf_counter() - t0
+
+    B = max(64, 8 * cores)
+    probe = run(B, 2)
+    T = int(max(2, min(64, seconds_target / max(probe / 2, 1e-6))))
+    sec = run(B, T)
+    return B * T / sec, cores, f"1 layer, {B} chunks x {T} timesteps, H={H}, R={R}, OpenMP over chunks"
+
+
+# ---- GPU arm ----------------------------------------------------------------------------------------
+
+def time_rotating(calls, iters, torch):
+    """calls: list of zero-arg launchers on disjoint buffers (total footprint > L2); returns the
+    mean milliseconds per call over `iters` rounds, CUDA events on the current stream."""
+    for c in calls:
+        c()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        for c in calls:
+            c()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (iters * len(calls))
+
+
+def bench_ops(torch, peaks):
+    """Configs 1-4 of the path; each entry reports time, achieved GB/s or TOP/s and the fraction
+    of the measured HBM copy bandwidth (frac_hbm) that the algorithmic bytes imply."""
+    from fluke_b200 import ops, prep
+    dev = "cuda"
+    out = {}
+    g = torch.Generator().manual_seed(0)
+    hbm = peaks["hbm_gbs"]
+
+    def entry(ms, bytes_, ops_=None):
+        e = {"us": round(ms * 1e3, 2), "GBps": round(bytes_ / ms / 1e6, 1), "frac_hbm": round(bytes_ / ms / 1e6 / hbm, 3)}
+        if ops_:
+            e["TOPs"] = round(ops_ / ms / 1e9, 1)
+        return e
+
+    # config 1: rotary on q,k of [32,1000,3,8,64]
+    sin, cos = prep.rotary_tables(1000, 64, device=dev)
+    qs = [torch.randn(32, 1000, 3, 8, 64, generator=g).half().to(dev) for _ in range(4)]
+    ms = time_rotating([lambda q=q: ops.rotary_qkv_(q, sin, cos, 32) for q in qs], 20, torch)
+    out["rotary_cfg1"] = entry(ms, 131.33e6)
+    # config 2: rmsnorm (+quant) [32000,512]
+    n, h = 32000, 512
+    w = (1 + 0.1 * torch.randn(h, generator=g)).half().to(dev)
+    xs_ = [torch.randn(n, h, generator=g).half().to(dev) for _ in range(6)]
+    rs = [torch.randn(n, h, generator=g).half().to(dev) for _ in range(2)]
+    outs = [torch.empty(n, h, dtype=torch.float16, device=dev) for _ in range(2)]
+    ms = time_rotating([lambda i=i: ops.rmsnorm(xs_[i], rs[i % 2], w, 2.0, 1e-5, out=outs[i % 2]) for i in range(6)], 20, torch)
+    out["rmsnorm_cfg2"] = entry(ms, 98.31e6)
+    q8 = [torch.zeros(n, h, dtype=torch.int8, device=dev) for _ in range(6)]
+    s8 = [torch.ones(n, device=dev) for _ in range(6)]
+    ms = time_rotating([lambda i=i: ops.rmsnorm_quant_int8(xs_[i], w, q8[i], s8[i], 0.0, 1e-5) for i in range(6)], 20, torch)
+    out["rmsnorm_quant_int8_cfg2"] = entry(ms, 65.79e6)
+    # config 3: QKV int8 GEMM + rotary, M=32000
+    be = ops.int8_select(0)
+    a8 = [prep.quantize_int8_rows(torch.randn(n, 512, generator=g)) for _ in range(3)]
+    a8 = [(a.to(dev), s.to(dev)) for a, s in a8]
+    wq, sq = prep.quantize_int8_rows(torch.randn(1536, 512, generator=g) * 0.02)
+    wq, sq = wq.to(dev), sq.to(dev)
+    o3 = [torch.empty(n, 1536, dtype=torch.float16, device=dev) for _ in range(3)]
+    ms = time_rotating([lambda i=i: ops.qkv_rotary_i8(be, a8[i][0], wq, a8[i][1], sq, sin, cos, 1000, out=o3[i]) for i in range(3)], 20, torch)
+    out["qkv_rotary_i8_cfg3"] = entry(ms, 115.87e6, 2.0 * n * 1536 * 512)
+    # config 4: dual GEMM + SiLU
+    wg, sg = prep.quantize_int8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    wu, su = prep.quantize_int8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    wg, sg, wu, su = wg.to(dev), sg.to(dev), wu.to(dev), su.to(dev)
+    o4 = [torch.empty(n, 2048, dtype=torch.float16, device=dev) for _ in range(3)]
+    ms = time_rotating([lambda i=i: ops.gated_mlp_i8(be, a8[i][0], wg, wu, a8[i][1], sg, su, out=o4[i]) for i in range(3)], 20, torch)
+    out["gated_mlp_i8_cfg4"] = entry(ms, 149.7e6, 4.0 * n * 2048 * 512)
+    # fp8 variants of 3 and 4 (plain [N,K] weights)
+    be8 = ops.fp8_select(0)
+    f8 = [prep.quantize_fp8_rows(torch.randn(n, 512, generator=g)) for _ in range(3)]
+    f8 = [(a.view(torch.uint8).to(dev), s.to(dev)) for a, s in f8]
+    wq8, sq8 = prep.quantize_fp8_rows(torch.randn(1536, 512, generator=g) * 0.02)
+    wq8, sq8 = wq8.view(torch.uint8).to(dev), sq8.to(dev)
+    ms = time_rotating([lambda i=i: ops.qkv_rotary_fp8(be8, f8[i][0], wq8, f8[i][1], sq8, sin, cos, 1000, plain=True, out=o3[i]) for i in range(3)], 20, torch)
+    out["qkv_rotary_fp8_cfg3"] = entry(ms, 115.87e6, 2.0 * n * 1536 * 512)
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from fluke_b200 import lib as flib, ops, prep
+    from fluke_b200.lstm import FactoredLstmLayer, run_stack
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the library has no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    flib.load()
+    peaks = measured_peaks()
+
+    T, B, H, R, NL = T_STEPS, CHUNKS_PER_GPU, HIDDEN, RANK, LAYERS
+    gw = torch.Generator().manual_seed(42)                       # weights: identical on every rank
+    layers = [FactoredLstmLayer.random(H, R, bool(i % 2), gw, dev) for i in range(NL)]
+    gx = torch.Generator().manual_seed(1000 + rank)              # each rank's own chunks
+    x_host = torch.empty(T, B, H, dtype=torch.int8).pin_memory()
+    xs_host = torch.empty(T * B, dtype=torch.float32).pin_memory()
+    slab = 100                                                   # N(0,1) rows quantised per row (amax/127);
+    q, s = prep.quantize_int8_rows(torch.randn(slab * B, H, generator=gx))   # one slab of timesteps, tiled over T
+    for t0 in range(0, T, slab):
+        x_host[t0:t0 + slab] = q.view(slab, B, H)
+        xs_host[t0 * B:(t0 + slab) * B] = s
+    x_dev, xs_dev = x_host.to(dev), xs_host.to(dev)
+    bufs = [torch.empty(T, B, H, dtype=torch.int8, device=dev) for _ in range(2)]
+    ws = torch.empty(flib.load().fluke_factored_lstm_layer_workspace(T, B, H, R), dtype=torch.uint8, device=dev)
+    out_host = torch.empty(T, B, H, dtype=torch.int8).pin_memory()
+
+    def fresh_state():
+        return [(torch.zeros(B, H, dtype=torch.float32, device=dev), torch.zeros(B, H, dtype=torch.int8, device=dev))
+                for _ in range(NL)]
+
+    def step_resident():
+        return run_stack(layers, x_dev, xs_dev, state=fresh_state(), workspace=ws, buffers=bufs)[0]
+
+    def step_e2e():
+        xd = x_dev.copy_(x_host, non_blocking=True)
+        sd = xs_dev.copy_(xs_host, non_blocking=True)
+        y = run_stack(layers, xd, sd, state=fresh_state(), workspace=ws, buffers=bufs)[0]
+        out_host.copy_(y, non_blocking=True)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return reduce_step_time(e0.elapsed_time(e1) / steps)
+
+    for _ in range(args.warmup):
+        step_resident()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(step_resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    status = flib.read_status()
+    if status != 0:
+        raise SystemExit(f"bench.py: device status word {status:#x}: a bounded device wait gave up")
+
+    units = local_units(B, T, NL) * world
+    value = units / (ms * 1e-3)
+    e2e_value = units / (ms_e2e * 1e-3)
+
+    line = None
+    if rank == 0:
+        # dominant kernel alone: the fused step of layer 0, T launches back to back
+        st = fresh_state()[0]
+        lay = layers[0]
+
+        def only(mask):
+            ops.factored_lstm_layer_i8(x_dev, xs_dev, lay.dn_ih, lay.dn_ih_scale, lay.dn_hh, lay.dn_hh_scale, lay.w_up,
+                                       lay.bias, st[0], st[1], h_out=bufs[0], workspace=ws, phase_mask=mask)
+        per_kernel = {}
+        for name, mask, launches in (("lstm_step_kernel", 4, T), ("down_proj_gemm", 2, T), ("x_down_gemm", 1, 1)):
+            only(mask)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                only(mask)
+            e1.record()
+            torch.cuda.synchronize()
+            per_kernel[name] = e0.elapsed_time(e1) / (3 * launches) * 1e3   # microseconds per launch
+        flops = 2.0 * B * (2 * R) * (4 * H)
+        achieved = flops / (per_kernel["lstm_step_kernel"] * 1e-6) / 1e12
+        roofline = {"kernel": "lstm_step_kernel", "bound": "tensor", "achieved": round(achieved, 2),
+                    "peak": peaks["tf_sustained"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tf_sustained"], 4),
+                    "peak_source": f"{peaks['source']} bf16 GEMM, sustained", "traffic": None,
+                    "flops_per_launch": flops, "us_per_launch": {k: round(v, 3) for k, v in per_kernel.items()}}
+        cpu_v, cores, sample = cpu_lstm_sample()
+        ops_res = bench_ops(torch, peaks) if world == 1 or True else {}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f16",
+            "data": "synthetic",
+            "config": {"workload": "factored int8 LSTM stack: 5 layers alternating direction, T=1000, H=768, rank=128, "
+                                   f"{B} chunks per GPU", "l2": "inputs larger than L2 (786 MB per layer input)",
+                       "parallelism": f"dp{world} (independent chunks, no collective)"},
+            "timesteps_per_sec_per_gpu_per_layer": T * NL / (ms * 1e-3),
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() + xs_host.numel() * 4, "d2h_bytes_per_step": out_host.numel()},
+            "gpu_launches": args.steps * NL * (1 + 2 * T),
+            "clocks": clocks, "roofline": roofline,
+            "cpu_baseline": {"value": cpu_v, "unit": "chunk-timesteps/s (per layer)", "cores": cores, "kind": "port",
+                             "sample": sample},
+            "ops": ops_res,
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    per_step = max(3.0, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        v, cores, sample = cpu_lstm_sample(per_step)
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    B, T, NL = CHUNKS_PER_GPU, T_STEPS, LAYERS
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": local_units(B, T, NL) / value * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8+f16", "data": "synthetic",
+        "config": {"workload": "factored int8 LSTM stack: 5 layers alternating direction, T=1000, H=768, rank=128, "
+                               f"{B} chunks per GPU", "note": "CPU arm: bounded sample per step, rate extrapolated"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

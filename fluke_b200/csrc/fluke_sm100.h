@@ -116,6 +116,9 @@ int fluke_sm100_lstm_step(const fluke_sm100_lstm_step_t *s, void *stream);
  * the public fluke_flstm_layer_t of <fluke/fluke.h>. */
 size_t fluke_sm100_lstm_layer_workspace(int T, int B, int H, int R);
 int fluke_sm100_lstm_layer(const void *layer /* const fluke_flstm_layer_t* */, void *stream);
+/* Launch only some kernel classes of the layer: 1 = x_down GEMM, 2 = per-step down-projection,
+ * 4 = per-step fused step (7 = the layer). For timing one class alone. */
+int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, void *stream);
 
 #ifdef __cplusplus
 }

@@ -391,16 +391,17 @@ inline int device_sm_count() {
     return cached[dev];
 }
 
-// Raises the dynamic shared-memory limit of `kernel` once per device.
-template <typename K>
-int configure_smem(K kernel, int bytes) {
+// Raises the dynamic shared-memory limit of KERNEL once per device. The kernel is a template
+// argument so that every instantiation keeps its own "done" flags.
+template <auto KERNEL>
+int configure_smem(int bytes) {
     static bool done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!done[dev]) {
         cudaError_t e =
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+            cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         if (e != cudaSuccess) return (int)e;
         done[dev] = true;
     }
@@ -458,7 +459,7 @@ template <int KIND, int EPI, int BN_MMA, int STAGES>
 int plan_launch(const GemmPlan &plan, int a_plane, cudaStream_t stream) {
     using L = SmemLayout<BN_MMA, STAGES>;
     auto kernel = gemm_kernel<KIND, EPI, BN_MMA, STAGES>;
-    int rc = configure_smem(kernel, L::kDynamic);
+    int rc = configure_smem<gemm_kernel<KIND, EPI, BN_MMA, STAGES>>(L::kDynamic);
     if (rc) return rc;
     if (plan.grid == 0) return 0;
     GemmDev p = plan.p;

@@ -305,7 +305,10 @@ extern "C" size_t fluke_sm100_lstm_layer_workspace(int T, int B, int H, int R) {
     return align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024);
 }
 
-extern "C" int fluke_sm100_lstm_layer(const void *layer, void *stream_) {
+// phase_mask selects which kernel classes are launched: 1 = x_down GEMM, 2 = per-step
+// down-projection, 4 = per-step fused step. 7 is the layer; other masks exist so a benchmark
+// can time one kernel class alone (their outputs are not a valid layer result).
+extern "C" int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, void *stream_) {
     using namespace fluke_sm100;
     const fluke_flstm_layer_t *l = static_cast<const fluke_flstm_layer_t *>(layer);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -325,7 +328,7 @@ extern "C" int fluke_sm100_lstm_layer(const void *layer, void *stream_) {
     int rc;
 
     // 1. x_down[t] = down_proj(x[t], dn_ih) for every timestep, as one GEMM with M = T*B.
-    {
+    if (phase_mask & 1) {
         fluke_sm100_gemm_t g = {};
         g.kind = FLUKE_SM100_KIND_I8; g.epilogue = FLUKE_SM100_EPI_DEQUANT;
         g.M = T * B; g.N = R; g.K = H;
@@ -374,16 +377,23 @@ extern "C" int fluke_sm100_lstm_layer(const void *layer, void *stream_) {
     int t_prev = -1;
     for (int i = 0; i < T; ++i) {
         const int t = l->reverse ? T - 1 - i : i;
-        if (i == 0)
+        rc = 0;
+        if (!(phase_mask & 2)) {
+        } else if (i == 0) {
             rc = plan_launch<kKindI8, FLUKE_SM100_EPI_DEQUANT, kPlainBN, kPlainStages>(dp_first, 0, stream);
-        else
+        } else {
             rc = plan_launch<kKindI8, FLUKE_SM100_EPI_DEQUANT, kPlainBN, kPlainStages>(dp_rest, t_prev, stream);
+        }
         if (rc) return rc;
-        rc = lstm_plan_launch(step, 0, t, h_out + size_t(t) * B * H, stream);
+        if (phase_mask & 4) rc = lstm_plan_launch(step, 0, t, h_out + size_t(t) * B * H, stream);
         if (rc) return rc;
         t_prev = t;
     }
     // 4. final hidden state
     return (int)cudaMemcpyAsync(l->h_i8, h_out + size_t(t_prev) * B * H, size_t(B) * H,
                                 cudaMemcpyDeviceToDevice, stream);
+}
+
+extern "C" int fluke_sm100_lstm_layer(const void *layer, void *stream) {
+    return fluke_sm100_lstm_layer_phases(layer, 7, stream);
 }

@@ -390,6 +390,9 @@ quant_rows_kernel(const __half *__restrict__ in, uint8_t *__restrict__ out,
 }
 
 // ---- rotary embedding (nn_kernel_cuda.h:35-69) -------------------------------------------------
+// The reference's nvcc build evaluates the two outputs as fma(x0,cos,-(x1*sin)) and
+// fma(x0,sin,x1*cos) (established by comparing its kernel's output bits with each candidate);
+// the same order is spelled out with intrinsics here so it does not depend on the compiler.
 // Vector path: one thread rotates 8 pairs (x0 = 16 bytes at offset 8c, x1 = 16 bytes at offset
 // W + 8c). With 8 heads of 64 and W = 32 a warp covers one (batch, position) row of 1 KB.
 __global__ void __launch_bounds__(256)
@@ -420,13 +423,13 @@ rotary_vec_kernel(__half *x, const float *__restrict__ sin_tab, const float *__r
     for (int k = 0; k < 4; ++k) {
         {
             const float x0 = a[k].x, x1 = bq[k].x, cos = cosv[2 * k], sin = sinv[2 * k];
-            o0[k].x = x0 * cos - x1 * sin;
-            o1[k].x = x0 * sin + x1 * cos;
+            o0[k].x = __fmaf_rn(x0, cos, -__fmul_rn(x1, sin));
+            o1[k].x = __fmaf_rn(x0, sin, __fmul_rn(x1, cos));
         }
         {
             const float x0 = a[k].y, x1 = bq[k].y, cos = cosv[2 * k + 1], sin = sinv[2 * k + 1];
-            o0[k].y = x0 * cos - x1 * sin;
-            o1[k].y = x0 * sin + x1 * cos;
+            o0[k].y = __fmaf_rn(x0, cos, -__fmul_rn(x1, sin));
+            o1[k].y = __fmaf_rn(x0, sin, __fmul_rn(x1, cos));
         }
     }
     // __float2half rounds to nearest even, as does the paired conversion used by pack8.
@@ -450,8 +453,8 @@ rotary_scalar_kernel(__half *x, const float *__restrict__ sin_tab,
     __half *o1 = o0 + width;
     const float cos = cos_tab[int64_t(s) * width + rot], sin = sin_tab[int64_t(s) * width + rot];
     const float x0 = __half2float(*o0), x1 = __half2float(*o1);
-    *o0 = __float2half(x0 * cos - x1 * sin);
-    *o1 = __float2half(x0 * sin + x1 * cos);
+    *o0 = __float2half(__fmaf_rn(x0, cos, -__fmul_rn(x1, sin)));
+    *o1 = __float2half(__fmaf_rn(x0, sin, __fmul_rn(x1, cos)));
 }
 
 // ---- SiLU-multiply (nn_kernel_cuda.h:71-90) -----------------------------------------------------
@@ -485,14 +488,16 @@ silu_mul_kernel(const __half *__restrict__ in, __half *__restrict__ out, int64_t
 }
 
 // ---- LSTM gate epilogue on f16 (nn_kernel_cuda.h:233-255) ----------------------------------------
+// Operation order of the reference's nvcc build, spelled out: gates fma(g, 0.2, 0.5), cell
+// fma(i, g~, f*c) (established by comparing its kernel's output bits with each candidate).
 __device__ __forceinline__ void flstm_gate(float gi, float gf, float gg, float go, float c_old,
                                            float &c_new, float &h_new) {
-    const float i_g = fmaxf(0.f, fminf(1.f, gi * 0.2f + 0.5f));
-    const float f_g = fmaxf(0.f, fminf(1.f, gf * 0.2f + 0.5f));
+    const float i_g = fmaxf(0.f, fminf(1.f, __fmaf_rn(gi, 0.2f, 0.5f)));
+    const float f_g = fmaxf(0.f, fminf(1.f, __fmaf_rn(gf, 0.2f, 0.5f)));
     const float g_g = fmaxf(-1.f, fminf(1.f, gg));
-    const float o_g = fmaxf(0.f, fminf(1.f, go * 0.2f + 0.5f));
-    c_new = f_g * c_old + i_g * g_g;
-    h_new = o_g * tanhf(c_new);
+    const float o_g = fmaxf(0.f, fminf(1.f, __fmaf_rn(go, 0.2f, 0.5f)));
+    c_new = __fmaf_rn(i_g, g_g, __fmul_rn(f_g, c_old));
+    h_new = __fmul_rn(o_g, tanhf(c_new));
 }
 
 template <int VEC>

@@ -241,8 +241,9 @@ def factored_lstm_step_i8(A, W4, bias4, c, h_out=None):
 
 
 def factored_lstm_layer_i8(x_i8, x_scale, dn_ih, dn_ih_scale, dn_hh, dn_hh_scale, w_up, bias, c, h,
-                           reverse=False, h_out=None, workspace=None):
-    """One layer over x_i8 [T,B,H]; c (f32 [B,H]) and h (int8 [B,H]) are state, updated in place."""
+                           reverse=False, h_out=None, workspace=None, phase_mask=7):
+    """One layer over x_i8 [T,B,H]; c (f32 [B,H]) and h (int8 [B,H]) are state, updated in place.
+    phase_mask != 7 launches only some kernel classes (timing aid, see fluke.h)."""
     _dev(x_i8, x_scale, dn_ih, dn_ih_scale, dn_hh, dn_hh_scale, w_up, bias, c, h)
     t, b, hd = x_i8.shape
     r = dn_ih.size(0)
@@ -254,5 +255,9 @@ def factored_lstm_layer_i8(x_i8, x_scale, dn_ih, dn_ih_scale, dn_hh, dn_hh_scale
                                      _p(dn_ih), _p(dn_ih_scale), _p(dn_hh), _p(dn_hh_scale),
                                      _p(w_up), _p(bias), _p(c), _p(h), _p(h_out),
                                      _p(workspace), workspace.numel())
-    _check(_L().fluke_factored_lstm_layer_i8_gpu(ctypes.byref(layer)), "fluke_factored_lstm_layer_i8_gpu")
+    if phase_mask == 7:
+        _check(_L().fluke_factored_lstm_layer_i8_gpu(ctypes.byref(layer)), "fluke_factored_lstm_layer_i8_gpu")
+    else:
+        _check(_L().fluke_factored_lstm_layer_phases_gpu(ctypes.byref(layer), phase_mask),
+               "fluke_factored_lstm_layer_phases_gpu")
     return h_out

@@ -376,6 +376,12 @@ typedef struct {
 size_t fluke_factored_lstm_layer_workspace(int T, int B, int H, int R);
 int fluke_factored_lstm_layer_i8_gpu(const fluke_flstm_layer_t *layer);
 
+/* Measurement aid: launch only some kernel classes of the layer so one class can be timed
+ * alone. phase_mask bits: 1 = x_down GEMM, 2 = per-step down-projection, 4 = per-step fused
+ * step; 7 is fluke_factored_lstm_layer_i8_gpu. With any other mask the outputs are not a
+ * layer result. */
+int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int phase_mask);
+
 #endif /* HAVE_CUDA || HAVE_ROCM */
 
 #ifdef __cplusplus

@@ -59,7 +59,7 @@ def _call(name, *args):
     fn(*conv)
 
 
-def set_fma_modes(sumsq=1, resadd=1, rot_lo=1, rot_hi=1, gate=1, cell=1):
+def set_fma_modes(sumsq=1, resadd=1, rot_lo=1, rot_hi=1, gate=1, cell=2):
     _call("orc_set_fma_modes", sumsq, resadd, rot_lo, rot_hi, gate, cell)
 
 

@@ -45,3 +45,8 @@ int fluke_factored_lstm_layer_i8_gpu(const fluke_flstm_layer_t *layer) {
     if (!layer) return -1;
     return fluke_host_note_error(fluke_sm100_lstm_layer(layer, fluke_host_stream()));
 }
+
+int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int phase_mask) {
+    if (!layer) return -1;
+    return fluke_host_note_error(fluke_sm100_lstm_layer_phases(layer, phase_mask, fluke_host_stream()));
+}
