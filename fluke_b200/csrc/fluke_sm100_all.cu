@@ -4,3 +4,4 @@
 #include "rowwise_sm100.cu"
 #include "gemm_sm100.cu"
 #include "lstm_sm100.cu"
+#include "lstm_noalloc_sm100.cu"

@@ -74,6 +74,7 @@ SIGNATURES = {
     "fluke_factored_lstm_layer_workspace": (Z, [I, I, I, I]),
     "fluke_factored_lstm_layer_i8_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t)]),
     "fluke_factored_lstm_layer_phases_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t), I]),
+    "fluke_factored_lstm_layer_i8_noalloc_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t)]),
     # internal status word (bounded device waits)
     "fluke_sm100_read_status": (I, [ctypes.POINTER(ctypes.c_uint), I]),
 }

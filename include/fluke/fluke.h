@@ -382,6 +382,18 @@ int fluke_factored_lstm_layer_i8_gpu(const fluke_flstm_layer_t *layer);
  * layer result. */
 int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int phase_mask);
 
+/* No counterpart in the reference. The same layer as fluke_factored_lstm_layer_i8_gpu for
+ * callers that cannot allocate device memory (inside a stream capture, plug-ins without an
+ * allocator, fixed memory budgets): layer->workspace / workspace_bytes are ignored and the
+ * intermediates live in a FLUKE_LSTM_NOALLOC_SCRATCH_BYTES array built into the library, held
+ * by every GPU that loads it. Nothing is allocated. The layer must satisfy
+ * fluke_factored_lstm_layer_workspace(T,B,H,R) <= FLUKE_LSTM_NOALLOC_SCRATCH_BYTES, otherwise
+ * a message is printed and non-zero returned. The first call on a device resolves the array's
+ * device address: make it outside any stream capture. All calls share the array, so calls
+ * whose kernels overlap on the GPU race; run one such layer at a time per device. */
+#define FLUKE_LSTM_NOALLOC_SCRATCH_BYTES (4u << 20)
+int fluke_factored_lstm_layer_i8_noalloc_gpu(const fluke_flstm_layer_t *layer);
+
 #endif /* HAVE_CUDA || HAVE_ROCM */
 
 #ifdef __cplusplus
