@@ -119,6 +119,9 @@ int fluke_sm100_lstm_layer(const void *layer /* const fluke_flstm_layer_t* */, v
 /* Launch only some kernel classes of the layer: 1 = x_down GEMM, 2 = per-step down-projection,
  * 4 = per-step fused step (7 = the layer). For timing one class alone. */
 int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, void *stream);
+/* 1 (default): run the recurrence of a layer as persistent cooperative launches when the shape
+ * is covered (R = 128, H a multiple of 128 up to 1024); 0: always two launches per timestep. */
+void fluke_sm100_set_lstm_persistent(int enabled);
 
 #ifdef __cplusplus
 }

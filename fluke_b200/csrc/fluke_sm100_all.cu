@@ -4,4 +4,5 @@
 #include "rowwise_sm100.cu"
 #include "gemm_sm100.cu"
 #include "lstm_sm100.cu"
+#include "lstm_persist_sm100.cu"
 #include "lstm_noalloc_sm100.cu"

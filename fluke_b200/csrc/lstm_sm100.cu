@@ -296,13 +296,18 @@ extern "C" int fluke_sm100_lstm_step(const fluke_sm100_lstm_step_t *s, void *str
 
 // ---- whole layer --------------------------------------------------------------------------------
 
+extern "C" int fluke_sm100_lstm_layer_persistent(const void *layer, const void *x_down, void *hh_down,
+                                                 void *flags, void *stream);
+static int g_lstm_persistent = 1;
+extern "C" void fluke_sm100_set_lstm_persistent(int enabled) { g_lstm_persistent = enabled ? 1 : 0; }
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 extern "C" size_t fluke_sm100_lstm_layer_workspace(int T, int B, int H, int R) {
     (void)H;
     if (T <= 0 || B <= 0 || R <= 0) return 0;
-    // hh_down f16 [B,R] followed by x_down f16 [T,B,R]
-    return align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024);
+    // hh_down f16 [B,R], x_down f16 [T,B,R], then 1 KB of exchange counters
+    return align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024) + 1024;
 }
 
 // phase_mask selects which kernel classes are launched: 1 = x_down GEMM, 2 = per-step
@@ -339,7 +344,19 @@ extern "C" int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, 
         if (rc) return rc;
     }
 
-    // 2. plans of the per-step kernels (tensor maps are built once; t is a plane coordinate)
+    // 2. the recurrence in persistent launches where the shape allows it
+    if (phase_mask == 7 && g_lstm_persistent) {
+        void *flags = ws + align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024);
+        rc = fluke_sm100_lstm_layer_persistent(l, x_down, hh_down, flags, stream);
+        if (rc == 0) {
+            const int t_last = l->reverse ? 0 : T - 1;
+            return (int)cudaMemcpyAsync(l->h_i8, static_cast<int8_t *>(l->h_out_i8) + size_t(t_last) * B * H,
+                                        size_t(B) * H, cudaMemcpyDeviceToDevice, stream);
+        }
+        if (rc != -2) return rc;
+    }
+
+    // 3. otherwise: plans of the per-step kernels (tensor maps built once; t is a plane coordinate)
     GemmPlan dp_first, dp_rest;
     {
         fluke_sm100_gemm_t g = {};
@@ -372,7 +389,7 @@ extern "C" int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, 
         if (rc) return rc;
     }
 
-    // 3. the recurrence
+    // 4. the recurrence, two launches per timestep
     int8_t *h_out = static_cast<int8_t *>(l->h_out_i8);
     int t_prev = -1;
     for (int i = 0; i < T; ++i) {
@@ -389,7 +406,7 @@ extern "C" int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, 
         if (rc) return rc;
         t_prev = t;
     }
-    // 4. final hidden state
+    // 5. final hidden state
     return (int)cudaMemcpyAsync(l->h_i8, h_out + size_t(t_prev) * B * H, size_t(B) * H,
                                 cudaMemcpyDeviceToDevice, stream);
 }

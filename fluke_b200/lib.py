@@ -61,6 +61,7 @@ SIGNATURES = {
     "fluke_gated_mlp_fp8_gpu": (I, [P, P, P, P, P, P, P, P, I]),
     # additive
     "fluke_set_stream": (None, [P]),
+    "fluke_set_lstm_persistent": (None, [I]),
     "fluke_get_stream": (P, []),
     "fluke_last_error": (ctypes.c_char_p, []),
     "fluke_gemm_i8_gpu": (I, [P, P, P, P, F, P, I, I, I]),

@@ -376,6 +376,13 @@ typedef struct {
 size_t fluke_factored_lstm_layer_workspace(int T, int B, int H, int R);
 int fluke_factored_lstm_layer_i8_gpu(const fluke_flstm_layer_t *layer);
 
+/* How fluke_factored_lstm_layer_i8_gpu runs the recurrence: 1 (default) = one persistent launch
+ * per layer with the gate weights in shared memory and the cell state in registers for all T
+ * timesteps, when the shape is covered (R = 128, H a multiple of 128 up to 1024) and the device
+ * can co-schedule its CTAs; 0 = always two launches per timestep. Both give the same int8
+ * outputs within one code (the two K halves are accumulated in a different order). */
+void fluke_set_lstm_persistent(int enabled);
+
 /* Measurement aid: launch only some kernel classes of the layer so one class can be timed
  * alone. phase_mask bits: 1 = x_down GEMM, 2 = per-step down-projection, 4 = per-step fused
  * step; 7 is fluke_factored_lstm_layer_i8_gpu. With any other mask the outputs are not a

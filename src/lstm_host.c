@@ -50,3 +50,5 @@ int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int p
     if (!layer) return -1;
     return fluke_host_note_error(fluke_sm100_lstm_layer_phases(layer, phase_mask, fluke_host_stream()));
 }
+
+void fluke_set_lstm_persistent(int enabled) { fluke_sm100_set_lstm_persistent(enabled); }

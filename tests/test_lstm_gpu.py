@@ -18,6 +18,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=["persistent", "per_step"])
+def lstm_mode(request, flib):
+    """Runs a test once with the persistent layer kernel and once with two launches per step."""
+    flib.fluke_set_lstm_persistent(1 if request.param == "persistent" else 0)
+    yield request.param
+    flib.fluke_set_lstm_persistent(1)
+
+
 @pytest.mark.parametrize("B,H,Kc", [(256, 1024, 256), (128, 768, 256), (100, 768, 256), (200, 96, 128), (1, 64, 64), (1024, 768, 256)])
 def test_step_vs_oracle(B, H, Kc):
     g = torch.Generator().manual_seed(B + H)
@@ -77,7 +85,7 @@ def _run_oracle_layer(layer, x, xs, reverse, c0=None, h0=None):
 
 
 @pytest.mark.parametrize("T,B,reverse", [(12, 200, False), (12, 200, True), (40, 128, False), (3, 1, True)])
-def test_layer_vs_oracle(T, B, reverse):
+def test_layer_vs_oracle(T, B, reverse, lstm_mode):
     H, R = 768, 128
     layer, x, xs = _layer_case(T, B, H, R, 42 + T, reverse)
     c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
@@ -91,7 +99,7 @@ def test_layer_vs_oracle(T, B, reverse):
     assert torch.equal(h, ho[last])  # final hidden state = last written step
 
 
-def test_layer_resumes_from_state_and_fixed_scale_input():
+def test_layer_resumes_from_state_and_fixed_scale_input(lstm_mode):
     """Two halves run back to back (state carried in c/h) equal one run; input at the fixed
     1/127 scale (x_scale NULL) as for layers fed by a previous layer."""
     T, B, H, R = 10, 130, 768, 128
@@ -107,7 +115,7 @@ def test_layer_resumes_from_state_and_fixed_scale_input():
     assert np.abs(whole.cpu().numpy().astype(np.int32) - he.astype(np.int32)).max() <= 1
 
 
-def test_stack_alternating_directions_and_batch_shards():
+def test_stack_alternating_directions_and_batch_shards(lstm_mode):
     """3-layer stack (odd layer reversed): sharding the chunk axis over 2 'ranks' reproduces
     the unsharded output bit for bit; the stack agrees with the oracle stack within one code
     per layer input."""
@@ -133,7 +141,28 @@ def test_stack_alternating_directions_and_batch_shards():
     assert d.max() <= 2 and (d > 1).mean() < 1e-3 and (d != 0).mean() < 2e-2
 
 
-def test_layer_config_size_properties():
+def test_persistent_and_per_step_layers_agree(flib):
+    """Same layer through both drivers: the only difference is the accumulation order of the two
+    K halves, so codes differ by at most one, rarely. Also a hidden size of 1024 (64 units per CTA)
+    and a batch that is not a multiple of the 128-row tile."""
+    for (T, B, H) in [(16, 300, 768), (6, 130, 1024), (5, 1024, 768)]:
+        layer, x, xs = _layer_case(T, B, H, 128, 11 + B, False)
+        outs = []
+        for mode in (1, 0):
+            flib.fluke_set_lstm_persistent(mode)
+            c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
+            outs.append((ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh,
+                                                    layer.dn_hh_scale, layer.w_up, layer.bias, c, h).clone(), c, h))
+        flib.fluke_set_lstm_persistent(1)
+        d = (outs[0][0].int() - outs[1][0].int()).abs()
+        assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 5e-3
+        assert float((outs[0][1] - outs[1][1]).abs().max()) < 1e-2
+        he, ce, _ = _run_oracle_layer(layer, x, xs, False)
+        d = np.abs(outs[0][0].cpu().numpy().astype(np.int32) - he.astype(np.int32))
+        assert d.max() <= 1 and (d != 0).mean() < 5e-3
+
+
+def test_layer_config_size_properties(lstm_mode):
     """H = 768, R = 128, B = 1024 (T cut to 24): codes stay in [-127, 127], the first step of a
     zero state matches the single-step kernel on [0 | x_down], and the reversed layer on
     time-flipped input equals the flipped forward output."""
