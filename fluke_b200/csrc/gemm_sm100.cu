@@ -6,12 +6,14 @@
 //   warp 0      TMA producer: 128-byte-swizzled A and B tiles into a ring of smem stages
 //   warp 1      MMA issuer:   tcgen05.mma 128 x BN x 32B from shared-memory descriptors into
 //               one of two accumulator buffers in tensor memory
-//   warps 2-5   epilogue:     tcgen05.ld (thread = output row), dequant / rotary / SiLU in
+//   warps 2-9   epilogue:     two warps per TMEM lane quadrant, each owning half of the tile's
+//               columns: tcgen05.ld (thread = output row), dequant / rotary / SiLU in
 //               registers, f16 pack, swizzled smem staging, TMA tile store
 //
 // The two accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1; no
-// accumulator or f16 intermediate ever reaches HBM. It replaces TensorOpGemmI8
-// (cute/ampere/gemm/gemm_i8_quant.py:344-757), TensorOpGemmI8Rotary
+// accumulator or f16 intermediate ever reaches HBM. The rotary tables of a tile's 128 rows are
+// staged once per tile in shared memory (coalesced loads, swizzled rows) and read per head.
+// It replaces TensorOpGemmI8 (cute/ampere/gemm/gemm_i8_quant.py:344-757), TensorOpGemmI8Rotary
 // (cute/ampere/rotary/gemm_i8_rotary.py:151-472) and TensorOpDualGemmI8Silu
 // (cute/ampere/dual_gemm_silu/dual_gemm_i8_silu.py:150-523) of the reference, and follows
 // their epilogue arithmetic: acc*(sa*sb) for the base GEMM (:617,:750), (acc*sa)*sb for the
@@ -29,8 +31,9 @@ namespace {
 constexpr int kBlockM = 128;          // rows per tile = TMEM lanes
 constexpr int kBlockKBytes = 128;     // K bytes per stage = one swizzle row
 constexpr int kUmmaKBytes = 32;       // K bytes per tcgen05.mma
-constexpr int kNumThreads = 192;
+constexpr int kNumThreads = 320;
 constexpr int kEpilogueWarp0 = 2;
+constexpr int kEpilogueWarps = 8;
 constexpr int kStageRows = 32;        // rows per epilogue warp
 constexpr int kStagingBytes = kStageRows * 128;
 
@@ -46,20 +49,27 @@ struct GemmDev {
     int seqlen;
     int qk_cols;
     int a_plane;  // plane of the 3-D A tensor map this launch reads
+    long long *trace;  // optional: cycle counters of CTA 0 (development aid)
 };
 
-template <int BN_MMA, int STAGES>
+static long long *g_gemm_trace = nullptr;
+
+template <int EPI, int BN_MMA, int STAGES>
 struct SmemLayout {
+    static constexpr bool kRotary = (EPI == FLUKE_SM100_EPI_ROTARY);
+    static constexpr int kStagingBufs = kRotary ? 1 : 2;   // per epilogue warp
     static constexpr int kABytes = kBlockM * kBlockKBytes;
     static constexpr int kBBytes = BN_MMA * kBlockKBytes;
     static constexpr int kOffA = 0;
     static constexpr int kOffB = kOffA + STAGES * kABytes;
     static constexpr int kOffStaging = kOffB + STAGES * kBBytes;
-    static constexpr int kOffBars = kOffStaging + 4 * 2 * kStagingBytes;
-    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kOffTables = kOffStaging + kEpilogueWarps * kStagingBufs * kStagingBytes;
+    static constexpr int kOffBars = kOffTables + (kRotary ? 4 * 8192 : 0);  // per quadrant: sin 4 KB | cos 4 KB
+    static constexpr int kNumBars = 2 * STAGES + 4 + 8;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kTotal = kOffMisc + 16;
     static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
+    static_assert(kDynamic <= 232448, "shared memory budget of one CTA exceeded");
 };
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
@@ -88,14 +98,23 @@ __device__ __forceinline__ void stage_row(uint8_t *staging, uint32_t row, const 
     }
 }
 
+// Bounded barrier between the two epilogue warps of a lane quadrant (one arrival per warp).
+__device__ __forceinline__ bool pair_barrier(uint64_t *bar, uint32_t parity, int lane,
+                                             volatile int *abort_flag) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+    return mbar_wait(bar, parity, abort_flag, 5);
+}
+
 template <int KIND, int EPI, int BN_MMA, int STAGES>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_out,
             const GemmDev p) {
-    using L = SmemLayout<BN_MMA, STAGES>;
+    using L = SmemLayout<EPI, BN_MMA, STAGES>;
     constexpr bool kDual = (EPI == FLUKE_SM100_EPI_SILU);
     constexpr int BN_OUT = kDual ? BN_MMA / 2 : BN_MMA;  // output columns per tile
+    constexpr int kWarpCols = BN_OUT / 2;                // output columns per epilogue warp
     constexpr uint32_t kStageTxBytes = L::kABytes + L::kBBytes;
     constexpr uint32_t kTmemCols = 2 * BN_MMA;  // two accumulator buffers (256 or 512)
     constexpr uint32_t kIdesc = make_idesc<KIND>(kBlockM, BN_MMA);
@@ -108,6 +127,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     uint64_t *empty_bar = bars + STAGES;
     uint64_t *tfull_bar = bars + 2 * STAGES;
     uint64_t *tempty_bar = bars + 2 * STAGES + 2;
+    uint64_t *tab_full_bar = bars + 2 * STAGES + 4;   // [4] tables of the quadrant are staged
+    uint64_t *tab_empty_bar = bars + 2 * STAGES + 8;  // [4] both warps are done reading them
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kOffMisc + 4);
 
@@ -121,7 +142,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tfull_bar[s], 1);
-            mbar_init(&tempty_bar[s], 4);
+            mbar_init(&tempty_bar[s], kEpilogueWarps);
+        }
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(&tab_full_bar[s], 2);
+            mbar_init(&tab_empty_bar[s], 2);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -147,8 +172,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const int m0 = (tile / p.num_n_tiles) * kBlockM;
             const int n0 = (tile % p.num_n_tiles) * BN_OUT;
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                const long long tw0 = clock64();
                 ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, 1);
                 if (!ok) break;
+                if (p.trace && blockIdx.x == 0 && lane == 0) p.trace[0] += clock64() - tw0;
                 if (lane == 0) {
                     mbar_arrive_expect_tx(&full_bar[stage], kStageTxBytes);
                     uint8_t *sa = smem + L::kOffA + stage * L::kABytes;
@@ -181,13 +208,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
+            const long long tw1 = clock64();
             ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, 2);
             if (!ok) break;
+            if (p.trace && blockIdx.x == 0 && lane == 0) p.trace[1] += clock64() - tw1;
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + acc * BN_MMA;
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                const long long tw2 = clock64();
                 ok = mbar_wait(&full_bar[stage], phase, abort_flag, 3);
                 if (!ok) break;
+                if (p.trace && blockIdx.x == 0 && lane == 0) p.trace[2] += clock64() - tw2;
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint64_t adesc =
@@ -209,11 +240,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
-        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        const int q = warp & 3;                           // TMEM lane quadrant this warp may read
+        const int ch = (warp - kEpilogueWarp0) >> 2;      // which half of the tile's columns
         const int ew = warp - kEpilogueWarp0;
-        uint8_t *staging0 = smem + L::kOffStaging + ew * 2 * kStagingBytes;
+        uint8_t *staging0 = smem + L::kOffStaging + ew * L::kStagingBufs * kStagingBytes;
+        uint8_t *tables = smem + L::kOffTables + q * 8192;  // ROTARY only
         int local = 0;
         int store_idx = 0;
+        uint32_t tab_phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int m0 = (tile / p.num_n_tiles) * kBlockM;
@@ -228,35 +262,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 sa = p.scale_a ? (row_ok ? __ldg(p.scale_a + row) : 0.f) : p.const_scale_a;
             }
 
-            // Rotary tables of this row's position: 32 sin + 32 cos values, shared by every
-            // head of the tile.
-            float rs[32], rc[32];
+            // Rotary tables of the quadrant's 32 rows, staged once per tile: warp ch = 0 copies
+            // the sin rows, ch = 1 the cos rows (coalesced 16-byte loads, swizzled 128-byte rows).
             bool rotate = false;
             if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
                 rotate = n0 < p.qk_cols;
                 if (rotate) {
-                    const int pos = row_ok ? row % p.seqlen : 0;
-                    const float4 *s4 = reinterpret_cast<const float4 *>(p.sin_tab + pos * 32);
-                    const float4 *c4 = reinterpret_cast<const float4 *>(p.cos_tab + pos * 32);
+                    const float *src = ch == 0 ? p.sin_tab : p.cos_tab;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 s = __ldg(s4 + i), c = __ldg(c4 + i);
-                        rs[4 * i] = s.x; rs[4 * i + 1] = s.y; rs[4 * i + 2] = s.z; rs[4 * i + 3] = s.w;
-                        rc[4 * i] = c.x; rc[4 * i + 1] = c.y; rc[4 * i + 2] = c.z; rc[4 * i + 3] = c.w;
+                    for (int j = 0; j < 8; ++j) {
+                        const int id = j * 32 + lane;
+                        const int r = id >> 3, cc = id & 7;
+                        const int grow = m0 + q * 32 + r;
+                        const int pos = grow < p.M ? grow % p.seqlen : 0;
+                        const float4 v = __ldg(reinterpret_cast<const float4 *>(src + pos * 32) + cc);
+                        *reinterpret_cast<float4 *>(tables + ch * 4096 + sw128_offset(r, cc)) = v;
                     }
+                    ok = pair_barrier(&tab_full_bar[q], tab_phase, lane, abort_flag);
+                    if (!ok) break;
                 }
             }
 
+            const long long tw3 = clock64();
             ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 4);
             if (!ok) break;
+            const long long tw4 = clock64();
+            if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) { p.trace[3] += tw4 - tw3; p.trace[7] += 1; }
             tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA;
 
             constexpr int kChunkCols = (EPI == FLUKE_SM100_EPI_RAW) ? 32 : 64;
-            constexpr int kChunks = BN_OUT / kChunkCols;
+            constexpr int kChunks = kWarpCols / kChunkCols;
 #pragma unroll 1
-            for (int ch = 0; ch < kChunks; ++ch) {
-                const int c0 = ch * kChunkCols;
+            for (int chunk = 0; chunk < kChunks; ++chunk) {
+                const int c0 = ch * kWarpCols + chunk * kChunkCols;  // column inside the tile
                 const bool chunk_ok = n0 + c0 < p.N;  // N % 64 == 0: a chunk is all in or all out
                 uint32_t outw[32];  // one 128-byte output row segment
 
@@ -293,49 +332,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             outw[half * 16 + 2 * i + 1] = pack_half2(o[2], o[3]);
                         }
                     }
-                } else {
-                    // DEQUANT / DEQUANT2 / ROTARY: 64 columns = one head.
-                    uint32_t lo[32], hi[32];
-                    tmem_ld_32x32(t_row + c0, lo);
-                    tmem_ld_32x32(t_row + c0 + 32, hi);
-                    tmem_ld_wait();
-                    const float4 *sb_lo = reinterpret_cast<const float4 *>(p.scale_b + n0 + c0);
-                    const float4 *sb_hi = sb_lo + 8;
+                } else if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
+                    // One head: pairs (i, i+32). Two passes of 16 pairs keep the register count down.
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 bl = __ldg(sb_lo + i), bh = __ldg(sb_hi + i);
-                        const float blv[4] = {bl.x, bl.y, bl.z, bl.w};
-                        const float bhv[4] = {bh.x, bh.y, bh.z, bh.w};
-                        float o_lo[4], o_hi[4];
+                    for (int sub = 0; sub < 2; ++sub) {
+                        uint32_t lo[16], hi[16];
+                        tmem_ld_32x16(t_row + c0 + sub * 16, lo);
+                        tmem_ld_32x16(t_row + c0 + 32 + sub * 16, hi);
+                        tmem_ld_wait();
+                        const float4 *sb_lo = reinterpret_cast<const float4 *>(p.scale_b + n0 + c0 + sub * 16);
+                        const float4 *sb_hi = sb_lo + 8;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float a_lo = acc_to_float<KIND>(lo[4 * i + j]);
-                            const float a_hi = acc_to_float<KIND>(hi[4 * i + j]);
-                            if constexpr (EPI == FLUKE_SM100_EPI_DEQUANT) {
-                                o_lo[j] = a_lo * (sa * blv[j]);
-                                o_hi[j] = a_hi * (sa * bhv[j]);
-                            } else {
-                                const float x0 = (a_lo * sa) * blv[j];
-                                const float x1 = (a_hi * sa) * bhv[j];
-                                if (EPI == FLUKE_SM100_EPI_ROTARY && rotate) {
-                                    const float sn = rs[4 * i + j], cs = rc[4 * i + j];
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 bl = __ldg(sb_lo + i), bh = __ldg(sb_hi + i);
+                            const float blv[4] = {bl.x, bl.y, bl.z, bl.w};
+                            const float bhv[4] = {bh.x, bh.y, bh.z, bh.w};
+                            float snv[4] = {0.f, 0.f, 0.f, 0.f}, csv[4] = {1.f, 1.f, 1.f, 1.f};
+                            if (rotate) {
+                                const float4 s4 = *reinterpret_cast<const float4 *>(tables + sw128_offset(lane, sub * 4 + i));
+                                const float4 c4 = *reinterpret_cast<const float4 *>(tables + 4096 + sw128_offset(lane, sub * 4 + i));
+                                snv[0] = s4.x; snv[1] = s4.y; snv[2] = s4.z; snv[3] = s4.w;
+                                csv[0] = c4.x; csv[1] = c4.y; csv[2] = c4.z; csv[3] = c4.w;
+                            }
+                            float o_lo[4], o_hi[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float x0 = (acc_to_float<KIND>(lo[4 * i + j]) * sa) * blv[j];
+                                const float x1 = (acc_to_float<KIND>(hi[4 * i + j]) * sa) * bhv[j];
+                                if (rotate) {
                                     // fixed operation order (no compiler-chosen contraction)
-                                    o_lo[j] = __fmaf_rn(x0, cs, -__fmul_rn(x1, sn));
-                                    o_hi[j] = __fmaf_rn(x0, sn, __fmul_rn(x1, cs));
+                                    o_lo[j] = __fmaf_rn(x0, csv[j], -__fmul_rn(x1, snv[j]));
+                                    o_hi[j] = __fmaf_rn(x0, snv[j], __fmul_rn(x1, csv[j]));
                                 } else {
                                     o_lo[j] = x0;
                                     o_hi[j] = x1;
                                 }
                             }
+                            outw[sub * 8 + 2 * i] = pack_half2(o_lo[0], o_lo[1]);
+                            outw[sub * 8 + 2 * i + 1] = pack_half2(o_lo[2], o_lo[3]);
+                            outw[16 + sub * 8 + 2 * i] = pack_half2(o_hi[0], o_hi[1]);
+                            outw[16 + sub * 8 + 2 * i + 1] = pack_half2(o_hi[2], o_hi[3]);
                         }
-                        outw[2 * i] = pack_half2(o_lo[0], o_lo[1]);
-                        outw[2 * i + 1] = pack_half2(o_lo[2], o_lo[3]);
-                        outw[16 + 2 * i] = pack_half2(o_hi[0], o_hi[1]);
-                        outw[16 + 2 * i + 1] = pack_half2(o_hi[2], o_hi[3]);
+                    }
+                } else {
+                    // DEQUANT / DEQUANT2: 64 columns in two passes of 32
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t a[32];
+                        tmem_ld_32x32(t_row + c0 + half * 32, a);
+                        tmem_ld_wait();
+                        const float4 *sb4 = reinterpret_cast<const float4 *>(p.scale_b + n0 + c0 + half * 32);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 b = __ldg(sb4 + i);
+                            const float bv[4] = {b.x, b.y, b.z, b.w};
+                            float o[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float v = acc_to_float<KIND>(a[4 * i + j]);
+                                if constexpr (EPI == FLUKE_SM100_EPI_DEQUANT) o[j] = v * (sa * bv[j]);
+                                else o[j] = (v * sa) * bv[j];
+                            }
+                            outw[half * 16 + 2 * i] = pack_half2(o[0], o[1]);
+                            outw[half * 16 + 2 * i + 1] = pack_half2(o[2], o[3]);
+                        }
                     }
                 }
 
-                if (ch == kChunks - 1) {
+                if (chunk == kChunks - 1) {
                     // Every TMEM read of this accumulator is done: hand it back to the MMA warp
                     // before the slower store path.
                     tc_fence_before_sync();
@@ -344,9 +408,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
 
                 if (!chunk_ok) continue;
-                uint8_t *staging = staging0 + (store_idx & 1) * kStagingBytes;
-                if (lane == 0) tma_store_wait_read<1>();
+                uint8_t *staging = staging0 + (store_idx % L::kStagingBufs) * kStagingBytes;
+                const long long tw5 = clock64();
+                if (lane == 0) tma_store_wait_read<L::kStagingBufs - 1>();
                 __syncwarp();
+                if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) p.trace[4] += clock64() - tw5;
                 stage_row(staging, lane, outw);
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -355,6 +421,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     tma_store_commit();
                 }
                 ++store_idx;
+            }
+            if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) p.trace[5] += clock64() - tw4;
+            if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
+                if (rotate) {
+                    // both warps of the quadrant are done with the tables of this tile
+                    ok = pair_barrier(&tab_empty_bar[q], tab_phase, lane, abort_flag);
+                    tab_phase ^= 1u;
+                }
             }
         }
         if (lane == 0) tma_store_wait_all<0>();
@@ -369,6 +443,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
 }
 
+// ------------------------------------------------------------------------------------------
 // ------------------------------------------------------------------------------------------
 // Host side: a GemmPlan holds the tensor maps and kernel parameters of one problem; building
 // it costs four cuTensorMapEncodeTiled calls, launching it costs one kernel launch. Loops that
@@ -449,6 +524,7 @@ int plan_build(const fluke_sm100_gemm_t *g, int a_planes, GemmPlan *plan) {
     p.seqlen = g->seqlen > 0 ? g->seqlen : 1;
     p.qk_cols = g->qk_cols;
     p.a_plane = 0;
+    p.trace = g_gemm_trace;
     const int tiles = p.num_m_tiles * p.num_n_tiles;
     const int sms = device_sm_count();
     plan->grid = tiles < sms ? tiles : sms;
@@ -457,7 +533,7 @@ int plan_build(const fluke_sm100_gemm_t *g, int a_planes, GemmPlan *plan) {
 
 template <int KIND, int EPI, int BN_MMA, int STAGES>
 int plan_launch(const GemmPlan &plan, int a_plane, cudaStream_t stream) {
-    using L = SmemLayout<BN_MMA, STAGES>;
+    using L = SmemLayout<EPI, BN_MMA, STAGES>;
     auto kernel = gemm_kernel<KIND, EPI, BN_MMA, STAGES>;
     int rc = configure_smem<gemm_kernel<KIND, EPI, BN_MMA, STAGES>>(L::kDynamic);
     if (rc) return rc;
@@ -478,10 +554,10 @@ int launch(const fluke_sm100_gemm_t *g, cudaStream_t stream) {
     return plan_launch<KIND, EPI, BN_MMA, STAGES>(plan, 0, stream);
 }
 
-// Tile shapes: 128 x 128 with a 6-deep ring for the plain GEMMs; 128 x 256 (one UMMA of
-// N = 256 per K step) with a 4-deep ring for the two fused transformer kernels.
-constexpr int kPlainBN = 128, kPlainStages = 6;
-constexpr int kFusedBN = 256, kFusedStages = 4;
+// Tile shapes: 128 x 128 with a 4-deep ring for the plain GEMMs; 128 x 256 (one UMMA of
+// N = 256 per K step) with a 3-deep ring for the two fused transformer kernels.
+constexpr int kPlainBN = 128, kPlainStages = 4;
+constexpr int kFusedBN = 256, kFusedStages = 3;
 
 template <int KIND>
 int dispatch(const fluke_sm100_gemm_t *g, cudaStream_t s) {
@@ -517,6 +593,10 @@ extern "C" int fluke_sm100_gemm(const fluke_sm100_gemm_t *g, void *stream) {
     if (g->kind == FLUKE_SM100_KIND_I8) return dispatch<kKindI8>(g, s);
     if (g->kind == FLUKE_SM100_KIND_F8) return dispatch<kKindF8>(g, s);
     return (int)cudaErrorInvalidValue;
+}
+
+extern "C" void fluke_sm100_gemm_set_trace(void *device_buffer) {
+    fluke_sm100::g_gemm_trace = static_cast<long long *>(device_buffer);
 }
 
 extern "C" int fluke_sm100_compute_capability(int device_index) {

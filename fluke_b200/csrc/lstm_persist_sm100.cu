@@ -4,25 +4,31 @@
 // launch latencies every step. Here the whole recurrence of a layer runs in ONE cooperative
 // launch whose CTAs stay resident for all T timesteps:
 //
-//   gate CTAs   (row tile i of 128 chunks) x (slice j of UNITS hidden units). The slice's four
-//               gate weight blocks [4*UNITS, 2R] f16 stay in shared memory and the cell state
-//               of the slice stays in REGISTERS for the whole layer. Per step: the x_down half
-//               of the contraction is issued as soon as its (prefetched) tile is there, the
-//               hh_down half when the projected hidden state arrives; gates, cell update and
-//               the int8 hidden slice follow, written to h_out[t] and published with a flag.
-//   worker CTAs (row tile i) x (half of the R projection columns). The int8 down-projection
+//   gate CTAs   (PAIR of 128-chunk row tiles) x (slice of UNITS hidden units). The slice's four
+//               gate weight blocks [4*UNITS, 2R] f16 stay in shared memory; the cell state of
+//               the slice stays in REGISTERS for the whole layer. The two row tiles of the pair
+//               are independent recurrences that the CTA works on alternately, each with its own
+//               accumulator in tensor memory, its own operand buffers and its own four epilogue
+//               warps: while one tile's hidden state travels to the worker and back, the other
+//               tile computes. Per tile and step: the x_down half of the contraction is issued
+//               as soon as its tile is there, the hh_down half when the projected hidden state
+//               arrives; gates, cell update and the int8 hidden slice follow, written to h_out[t]
+//               and published with a counter.
+//   worker CTAs (row tile) x (half of the R projection columns). The int8 down-projection
 //               weights stay in shared memory. Per step: wait until all slices of the tile have
 //               published h_{t-1}, TMA-load the tile, tcgen05 kind::i8 contraction, scale,
 //               round to f16 (as the two-kernel form does) and publish hh_down[tile].
 //
 // Exchange between CTAs goes through L2 (h_out itself and a [B,R] f16 buffer) with per-tile
-// counters: writers store, __threadfence, CTA barrier, one atomic increment; readers poll with
-// ld.acquire, then fence.proxy.async before the TMA load of the freshly written data. The
-// launch is cooperative only to guarantee that all CTAs are co-resident (no grid.sync).
-// Every wait is bounded; a timeout raises a global abort word that all CTAs observe.
+// counters: writers store, meet at a CTA-scope barrier, then one thread fences at GPU scope and
+// increments the counter; readers poll with ld.acquire, then fence.proxy.async before the TMA
+// load of the freshly written data. The launch is cooperative only to guarantee that all CTAs
+// are co-resident (no grid.sync). Every wait is bounded; a timeout raises a global abort word
+// that all CTAs observe.
 //
-// Arithmetic is that of lstm_step_kernel and of the dequant GEMM epilogue; only the order in
-// which the two K halves are accumulated differs (x_down first).
+// Arithmetic is that of lstm_step_kernel and of the dequant GEMM epilogue, except that the two
+// K halves are accumulated x_down first and tanh is evaluated as 1 - 2/(exp(2c)+1) with the
+// fast exponential (absolute error ~1e-7, far below one int8 code).
 #include <fluke/fluke.h>
 
 #include "fluke_sm100.h"
@@ -34,17 +40,18 @@
 namespace fluke_sm100 {
 namespace {
 
-constexpr int kPThreads = 320;          // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
+constexpr int kPThreads = 320;          // warp 0 producer, warp 1 MMA, warps 2-5 / 6-9 epilogue
 constexpr int kPWorkersPerTile = 2;     // each projects R/2 = 64 columns
 constexpr int kPRank = 128;             // factor rank the kernel is built for
 constexpr int kPMaxHKB = 8;             // hidden K blocks of 128 bytes: H <= 1024
 constexpr int kPTmemCols = 256;
+constexpr int kPAccStride = 128;        // TMEM columns between the two tiles' accumulators
 
 struct PersistDev {
     int T, B, H;               // B: chunks handled by this launch
     int b_stride;              // chunks per timestep plane of h_out (the full batch)
     int reverse;
-    int n_tiles, n_slices;
+    int n_tiles, n_pairs, n_slices;
     int nkb_h;                 // H / 128
     const float *bias;         // [4H]
     const float *dn_scale;     // [R]
@@ -52,24 +59,30 @@ struct PersistDev {
     int8_t *h_out;             // [T,B,H]
     __half *hh_down;           // [B,R]
     unsigned int *flags;       // [0,n_tiles): h_ready, [n_tiles,2n_tiles): hh_ready, [2n_tiles]: abort
+    long long *trace;          // optional [T][8] SM-clock stamps of CTA 0 and of the first worker
 };
+
+// Development aid: when a trace buffer is set, the first gate CTA and the first worker CTA
+// record clock64() at the hand-over points of every step.
+static long long *g_persist_trace = nullptr;
 
 template <int UNITS>
 struct PersistSmem {
     // gate role
     static constexpr int kWKB = 4 * UNITS * 128;           // one K block of the four gate slices
     static constexpr int kOffW = 0;                         // 4 K blocks
-    static constexpr int kOffAhh = 4 * kWKB;                // 2 K blocks x 16 KB
-    static constexpr int kOffX = kOffAhh + 2 * 16384;       // 2 buffers x 2 K blocks x 16 KB
-    static constexpr int kGateBytes = kOffX + 4 * 16384;
+    static constexpr int kOffAhh = 4 * kWKB;                // per tile: 2 K blocks x 16 KB
+    static constexpr int kOffX = kOffAhh + 2 * 32768;       // per tile: 2 K blocks x 16 KB
+    static constexpr int kOffBias = kOffX + 2 * 32768;      // 4 x UNITS floats
+    static constexpr int kGateBytes = kOffBias + 4 * UNITS * 4;
     // worker role
     static constexpr int kDnKB = 64 * 128;                  // 64 projection rows x 128 B
     static constexpr int kOffDn = 0;
     static constexpr int kOffH = kPMaxHKB * kDnKB;
     static constexpr int kWorkerBytes = kOffH + kPMaxHKB * 16384;
-    static constexpr int kData = kGateBytes > kWorkerBytes ? kGateBytes : kWorkerBytes;
+    static constexpr int kData = ((kGateBytes > kWorkerBytes ? kGateBytes : kWorkerBytes) + 15) / 16 * 16;
     static constexpr int kOffBars = kData;
-    static constexpr int kNumBars = 16;
+    static constexpr int kNumBars = 24;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kDynamic = kOffMisc + 16 + 1024;
 };
@@ -79,6 +92,11 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned int ld_relaxed_u32(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 // Waits until *flag >= target. Gives up when the cycle limit passes or another CTA has raised
 // the global abort word; then raises both abort flags and returns false.
@@ -86,26 +104,39 @@ __device__ __forceinline__ bool wait_counter(const unsigned int *flag, unsigned 
                                              unsigned int *g_abort, volatile int *abort_flag,
                                              unsigned int site) {
     const long long t0 = clock64();
+    unsigned int spins = 0;
     for (;;) {
-        if (ld_acquire_u32(flag) >= target) return true;
+        // poll with relaxed loads; one acquire fence orders the data reads after the sighting
+        if (ld_relaxed_u32(flag) >= target) {
+            asm volatile("fence.acq_rel.gpu;" ::: "memory");
+            return true;
+        }
         if (*abort_flag) return false;
-        const bool late = clock64() - t0 > kWaitCycleLimit;
-        if (late || ld_acquire_u32(g_abort) != 0u) {
-            if (late) report_timeout(site);
-            *abort_flag = 1;
-            atomicExch(g_abort, 1u);
-            return false;
+        if ((++spins & 63u) == 0u) {
+            const bool late = clock64() - t0 > kWaitCycleLimit;
+            if (late || ld_acquire_u32(g_abort) != 0u) {
+                if (late) report_timeout(site);
+                *abort_flag = 1;
+                atomicExch(g_abort, 1u);
+                return false;
+            }
         }
     }
 }
 
-// Barrier over the eight epilogue warps built on an mbarrier so that, unlike bar.sync, the wait
-// is bounded: one arrival per warp, then every thread waits for the phase.
-__device__ __forceinline__ bool epi_barrier(uint64_t *bar, uint32_t parity, int lane,
-                                            volatile int *abort_flag) {
+// Barrier over a set of warps built on an mbarrier so that, unlike bar.sync, the wait is
+// bounded: one arrival per warp (release at CTA scope), then every thread waits for the phase.
+__device__ __forceinline__ bool warps_barrier(uint64_t *bar, uint32_t parity, int lane,
+                                              volatile int *abort_flag) {
     __syncwarp();
     if (lane == 0) mbar_arrive(bar);
     return mbar_wait(bar, parity, abort_flag, 60);
+}
+
+// Publishes everything the CTA's epilogue warps stored before their barrier: GPU-scope fence by
+// one thread (cumulative over the writes it observed through the barrier), then the increment.
+__device__ __forceinline__ void publish(unsigned int *counter) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
@@ -118,6 +149,9 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
 
 __device__ __forceinline__ float p_hard_sigmoid(float x) {
     return fmaxf(0.f, fminf(1.f, __fmaf_rn(x, 0.2f, 0.5f)));
+}
+__device__ __forceinline__ float p_tanh(float x) {
+    return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
 }
 __device__ __forceinline__ int p_quant_h(float h) {
     const float hs = __fmul_rn(h, 127.0f);
@@ -136,40 +170,35 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     const __grid_constant__ CUtensorMap tm_h0,   // h_0     [1,B,H] int8
                     const PersistDev p) {
     using L = PersistSmem<UNITS>;
-    constexpr int U2 = UNITS / 2;  // hidden units per epilogue thread
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kOffBars);
-    uint64_t *bar_once = &bars[0];      // resident weights loaded
-    uint64_t *bar_acc_full = &bars[1];  // MMAs of this step finished
-    uint64_t *bar_acc_empty = &bars[2]; // epilogue finished reading the accumulator
-    uint64_t *bar_x = &bars[3];         // [2] gate: x_down buffer filled
-    uint64_t *bar_ahh = &bars[5];       // gate: hh_down tile filled
-    uint64_t *bar_h = &bars[6];         // [kPMaxHKB] worker: h tile K block filled
-    uint64_t *bar_epi = &bars[14];      // epilogue warps have all stored their part of the step
+    uint64_t *bar_once = &bars[0];       // resident weights loaded
+    uint64_t *bar_acc_full = &bars[1];   // [2] MMAs of the tile's step finished
+    uint64_t *bar_acc_empty = &bars[3];  // [2] epilogue finished reading the accumulator
+    uint64_t *bar_x = &bars[5];          // [2] gate: x_down tile filled
+    uint64_t *bar_ahh = &bars[7];        // [2] gate: hh_down tile filled
+    uint64_t *bar_epi = &bars[9];        // [2] epilogue warps have stored their part of the step
+    uint64_t *bar_h = &bars[11];         // [kPMaxHKB] worker: h tile K block filled
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kOffMisc + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_gate = p.n_tiles * p.n_slices;
+    const int n_gate = p.n_pairs * p.n_slices;
     const bool is_gate = int(blockIdx.x) < n_gate;
-    const int tile = is_gate ? blockIdx.x / p.n_slices : (blockIdx.x - n_gate) / kPWorkersPerTile;
-    const int part = is_gate ? blockIdx.x % p.n_slices : (blockIdx.x - n_gate) % kPWorkersPerTile;
-    const int m0 = tile * 128;
-    unsigned int *h_ready = p.flags + tile;
-    unsigned int *hh_ready = p.flags + p.n_tiles + tile;
     unsigned int *g_abort = p.flags + 2 * p.n_tiles;
 
     if (threadIdx.x == 0) {
         mbar_init(bar_once, 1);
-        mbar_init(bar_acc_full, 1);
-        mbar_init(bar_acc_empty, 8);
-        mbar_init(&bar_x[0], 1);
-        mbar_init(&bar_x[1], 1);
-        mbar_init(bar_ahh, 1);
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(&bar_acc_full[g], 1);
+            mbar_init(&bar_acc_empty[g], is_gate ? 4 : 8);
+            mbar_init(&bar_x[g], 1);
+            mbar_init(&bar_ahh[g], 1);
+            mbar_init(&bar_epi[g], is_gate ? 4 : 8);
+        }
         for (int i = 0; i < kPMaxHKB; ++i) mbar_init(&bar_h[i], 1);
-        mbar_init(bar_epi, 8);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -182,7 +211,9 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
     auto time_of = [&](int i) { return p.reverse ? p.T - 1 - i : i; };
 
     if (is_gate) {
-        const int n0 = part * UNITS;
+        const int pair = blockIdx.x / p.n_slices;
+        const int n0 = (blockIdx.x % p.n_slices) * UNITS;
+        const int n_local = (2 * pair + 1 < p.n_tiles) ? 2 : 1;  // tiles this CTA really has
         if (warp == 0) {
             // ------------------------------ gate: producer ------------------------------
             if (lane == 0) {
@@ -194,26 +225,30 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     tma_load_2d(sw + 2 * UNITS * 128, &tm_w2, bar_once, kb * 64, n0);
                     tma_load_2d(sw + 3 * UNITS * 128, &tm_w3, bar_once, kb * 64, n0);
                 }
-                mbar_arrive_expect_tx(&bar_x[0], 2 * 16384);
-                tma_load_3d(smem + L::kOffX, &tm_x, &bar_x[0], 0, m0, time_of(0));
-                tma_load_3d(smem + L::kOffX + 16384, &tm_x, &bar_x[0], 64, m0, time_of(0));
                 bool ok = true;
                 for (int i = 0; i < p.T && ok; ++i) {
-                    // MMAs of step i-1 are done: its x buffer and the hh_down tile can be refilled
-                    if (i > 0) ok = mbar_wait(bar_acc_full, (i - 1) & 1, abort_flag, 32);
-                    if (!ok) break;
-                    if (i + 1 < p.T) {
-                        uint8_t *sx = smem + L::kOffX + ((i + 1) & 1) * 2 * 16384;
-                        mbar_arrive_expect_tx(&bar_x[(i + 1) & 1], 2 * 16384);
-                        tma_load_3d(sx, &tm_x, &bar_x[(i + 1) & 1], 0, m0, time_of(i + 1));
-                        tma_load_3d(sx + 16384, &tm_x, &bar_x[(i + 1) & 1], 64, m0, time_of(i + 1));
+                    for (int g = 0; g < n_local && ok; ++g) {
+                        const int m0 = (2 * pair + g) * 128;
+                        // MMAs of the tile's previous step are done: both operand buffers are free
+                        if (i > 0) ok = mbar_wait(&bar_acc_full[g], (i - 1) & 1, abort_flag, 32);
+                        if (!ok) break;
+                        uint8_t *sx = smem + L::kOffX + g * 32768;
+                        mbar_arrive_expect_tx(&bar_x[g], 32768);
+                        tma_load_3d(sx, &tm_x, &bar_x[g], 0, m0, time_of(i));
+                        tma_load_3d(sx + 16384, &tm_x, &bar_x[g], 64, m0, time_of(i));
                     }
-                    ok = wait_counter(hh_ready, (unsigned)(kPWorkersPerTile * (i + 1)), g_abort, abort_flag, 33);
-                    if (!ok) break;
-                    fence_proxy_async_all();
-                    mbar_arrive_expect_tx(bar_ahh, 2 * 16384);
-                    tma_load_3d(smem + L::kOffAhh, &tm_hh, bar_ahh, 0, m0, 0);
-                    tma_load_3d(smem + L::kOffAhh + 16384, &tm_hh, bar_ahh, 64, m0, 0);
+                    for (int g = 0; g < n_local && ok; ++g) {
+                        const int tile = 2 * pair + g;
+                        ok = wait_counter(p.flags + p.n_tiles + tile, (unsigned)(kPWorkersPerTile * (i + 1)),
+                                          g_abort, abort_flag, 33);
+                        if (!ok) break;
+                        if (p.trace && blockIdx.x == 0 && g == 0) p.trace[i * 8 + 0] = clock64();
+                        fence_proxy_async_all();
+                        uint8_t *sa = smem + L::kOffAhh + g * 32768;
+                        mbar_arrive_expect_tx(&bar_ahh[g], 32768);
+                        tma_load_3d(sa, &tm_hh, &bar_ahh[g], 0, tile * 128, 0);
+                        tma_load_3d(sa + 16384, &tm_hh, &bar_ahh[g], 64, tile * 128, 0);
+                    }
                 }
             }
             __syncwarp();
@@ -222,116 +257,139 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             constexpr uint32_t kIdesc = make_idesc<kKindF16>(128, 4 * UNITS);
             bool ok = mbar_wait(bar_once, 0, abort_flag, 34);
             for (int i = 0; i < p.T && ok; ++i) {
-                if (i > 0) ok = mbar_wait(bar_acc_empty, (i - 1) & 1, abort_flag, 35);
-                if (!ok) break;
-                ok = mbar_wait(&bar_x[i & 1], (i >> 1) & 1, abort_flag, 36);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (lane == 0) {
-                    const uint8_t *sx = smem + L::kOffX + (i & 1) * 2 * 16384;
-                    for (int kb = 0; kb < 2; ++kb) {  // x_down half: W K blocks 2, 3
-                        const uint64_t ad = make_smem_desc_sw128(smem_u32(sx + kb * 16384));
-                        const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffW + (2 + kb) * L::kWKB));
+                for (int g = 0; g < n_local && ok; ++g) {  // x_down halves: W K blocks 2, 3
+                    if (i > 0) ok = mbar_wait(&bar_acc_empty[g], (i - 1) & 1, abort_flag, 35);
+                    if (!ok) break;
+                    ok = mbar_wait(&bar_x[g], i & 1, abort_flag, 36);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+                        const uint8_t *sx = smem + L::kOffX + g * 32768;
+                        for (int kb = 0; kb < 2; ++kb) {
+                            const uint64_t ad = make_smem_desc_sw128(smem_u32(sx + kb * 16384));
+                            const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffW + (2 + kb) * L::kWKB));
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            tc_mma<kKindF16>(tmem_base, ad + uint64_t(2 * k), bd + uint64_t(2 * k), kIdesc,
-                                             (kb | k) != 0 ? 1u : 0u);
+                            for (int k = 0; k < 4; ++k)
+                                tc_mma<kKindF16>(tmem_base + g * kPAccStride, ad + uint64_t(2 * k),
+                                                 bd + uint64_t(2 * k), kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
-                ok = mbar_wait(bar_ahh, i & 1, abort_flag, 37);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (lane == 0) {
-                    for (int kb = 0; kb < 2; ++kb) {  // hh_down half: W K blocks 0, 1
-                        const uint64_t ad = make_smem_desc_sw128(smem_u32(smem + L::kOffAhh + kb * 16384));
-                        const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffW + kb * L::kWKB));
+                for (int g = 0; g < n_local && ok; ++g) {  // hh_down halves: W K blocks 0, 1
+                    ok = mbar_wait(&bar_ahh[g], i & 1, abort_flag, 37);
+                    if (!ok) break;
+                    if (p.trace && blockIdx.x == 0 && g == 0 && lane == 0) p.trace[i * 8 + 1] = clock64();
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+                        const uint8_t *sa = smem + L::kOffAhh + g * 32768;
+                        for (int kb = 0; kb < 2; ++kb) {
+                            const uint64_t ad = make_smem_desc_sw128(smem_u32(sa + kb * 16384));
+                            const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffW + kb * L::kWKB));
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            tc_mma<kKindF16>(tmem_base, ad + uint64_t(2 * k), bd + uint64_t(2 * k), kIdesc, 1u);
+                            for (int k = 0; k < 4; ++k)
+                                tc_mma<kKindF16>(tmem_base + g * kPAccStride, ad + uint64_t(2 * k),
+                                                 bd + uint64_t(2 * k), kIdesc, 1u);
+                        }
+                        tc_commit(&bar_acc_full[g]);
                     }
-                    tc_commit(bar_acc_full);
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         } else {
             // ------------------------------ gate: epilogue ------------------------------
+            const int g = (warp - 2) >> 2;  // which tile of the pair this warp set serves
             const int q = warp & 3;
-            const int chalf = (warp - 2) >> 2;
-            const int row = m0 + q * 32 + lane;
-            const bool row_ok = row < p.B;
-            const int u_base = n0 + chalf * U2;  // first hidden unit of this thread
-            float c[U2];
-            if (row_ok) {
+            const int tile = 2 * pair + g;
+            // stage the slice's biases in shared memory (read by every thread each step)
+            float *sbias = reinterpret_cast<float *>(smem + L::kOffBias);
+            for (int j = threadIdx.x - 64; j < 4 * UNITS; j += 256)
+                sbias[j] = __ldg(p.bias + (j / UNITS) * p.H + n0 + (j % UNITS));
+            asm volatile("bar.sync 2, 256;" ::: "memory");  // the eight epilogue warps, once, before any wait
+            if (g < n_local) {
+                const int row = tile * 128 + q * 32 + lane;
+                const bool row_ok = row < p.B;
+                float c[UNITS];
+                if (row_ok) {
 #pragma unroll
-                for (int v = 0; v < U2 / 4; ++v) {
-                    const float4 c4 = *reinterpret_cast<const float4 *>(p.c + int64_t(row) * p.H + u_base + 4 * v);
-                    c[4 * v] = c4.x; c[4 * v + 1] = c4.y; c[4 * v + 2] = c4.z; c[4 * v + 3] = c4.w;
-                }
-            } else {
-#pragma unroll
-                for (int v = 0; v < U2; ++v) c[v] = 0.f;
-            }
-            const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + chalf * U2;
-            bool ok = true;
-            for (int i = 0; i < p.T && ok; ++i) {
-                ok = mbar_wait(bar_acc_full, i & 1, abort_flag, 38);
-                if (!ok) break;
-                tc_fence_after_sync();
-                int8_t *hrow = p.h_out + (int64_t(time_of(i)) * p.b_stride + row) * p.H + u_base;
-#pragma unroll
-                for (int ch = 0; ch < U2 / 8; ++ch) {
-                    uint32_t gi[8], gf[8], gg[8], go[8];
-                    tmem_ld_32x8(t_row + 0 * UNITS + ch * 8, gi);
-                    tmem_ld_32x8(t_row + 1 * UNITS + ch * 8, gf);
-                    tmem_ld_32x8(t_row + 2 * UNITS + ch * 8, gg);
-                    tmem_ld_32x8(t_row + 3 * UNITS + ch * 8, go);
-                    tmem_ld_wait();
-                    if (ch == U2 / 8 - 1) {
-                        // all TMEM reads of this step are done: the next step's MMAs may overwrite
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_acc_empty);
+                    for (int v = 0; v < UNITS / 4; ++v) {
+                        const float4 c4 = *reinterpret_cast<const float4 *>(p.c + int64_t(row) * p.H + n0 + 4 * v);
+                        c[4 * v] = c4.x; c[4 * v + 1] = c4.y; c[4 * v + 2] = c4.z; c[4 * v + 3] = c4.w;
                     }
-                    uint32_t packed[2] = {0u, 0u};
+                } else {
 #pragma unroll
-                    for (int v = 0; v < 2; ++v) {
-                        const int u = u_base + ch * 8 + 4 * v;
-                        const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + 0 * p.H + u));
-                        const float4 bf = __ldg(reinterpret_cast<const float4 *>(p.bias + 1 * p.H + u));
-                        const float4 bg = __ldg(reinterpret_cast<const float4 *>(p.bias + 2 * p.H + u));
-                        const float4 bo = __ldg(reinterpret_cast<const float4 *>(p.bias + 3 * p.H + u));
-                        const float bis[4] = {bi.x, bi.y, bi.z, bi.w}, bfs[4] = {bf.x, bf.y, bf.z, bf.w};
-                        const float bgs[4] = {bg.x, bg.y, bg.z, bg.w}, bos[4] = {bo.x, bo.y, bo.z, bo.w};
+                    for (int v = 0; v < UNITS; ++v) c[v] = 0.f;
+                }
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + g * kPAccStride;
+                unsigned int *h_ready = p.flags + tile;
+                bool ok = true;
+                for (int i = 0; i < p.T && ok; ++i) {
+                    ok = mbar_wait(&bar_acc_full[g], i & 1, abort_flag, 38);
+                    if (!ok) break;
+                    if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) p.trace[i * 8 + 2] = clock64();
+                    tc_fence_after_sync();
+                    int8_t *hrow = p.h_out + (int64_t(time_of(i)) * p.b_stride + row) * p.H + n0;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int e = 4 * v + j;
-                            const float i_a = p_hard_sigmoid(__uint_as_float(gi[e]) + bis[j]);
-                            const float f_a = p_hard_sigmoid(__uint_as_float(gf[e]) + bfs[j]);
-                            const float o_a = p_hard_sigmoid(__uint_as_float(go[e]) + bos[j]);
-                            const float g_a = fmaxf(-1.f, fminf(1.f, __uint_as_float(gg[e]) + bgs[j]));
-                            const float c_new = __fmaf_rn(f_a, c[ch * 8 + e], __fmul_rn(i_a, g_a));
-                            c[ch * 8 + e] = c_new;
-                            const float h_new = o_a * tanhf(c_new);
-                            packed[v] |= (uint32_t(p_quant_h(h_new)) & 0xFFu) << (8 * j);
+                    for (int ch = 0; ch < UNITS / 8; ++ch) {
+                        uint32_t gi[8], gf[8], gg[8], go[8];
+                        tmem_ld_32x8(t_row + 0 * UNITS + ch * 8, gi);
+                        tmem_ld_32x8(t_row + 1 * UNITS + ch * 8, gf);
+                        tmem_ld_32x8(t_row + 2 * UNITS + ch * 8, gg);
+                        tmem_ld_32x8(t_row + 3 * UNITS + ch * 8, go);
+                        tmem_ld_wait();
+                        if (ch == UNITS / 8 - 1) {
+                            // all TMEM reads of this step are done: the next step's MMAs may overwrite
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&bar_acc_empty[g]);
                         }
-                    }
-                    if (row_ok) *reinterpret_cast<uint2 *>(hrow + ch * 8) = make_uint2(packed[0], packed[1]);
-                }
-                // publish this slice of h_t
-                __threadfence();
-                ok = epi_barrier(bar_epi, i & 1, lane, abort_flag);
-                if (ok && threadIdx.x == 64) atomicAdd(h_ready, 1u);
-            }
-            if (row_ok) {
+                        uint32_t packed[2] = {0u, 0u};
 #pragma unroll
-                for (int v = 0; v < U2 / 4; ++v)
-                    *reinterpret_cast<float4 *>(p.c + int64_t(row) * p.H + u_base + 4 * v) =
-                        make_float4(c[4 * v], c[4 * v + 1], c[4 * v + 2], c[4 * v + 3]);
+                        for (int v = 0; v < 2; ++v) {
+                            const int u = ch * 8 + 4 * v;
+                            const float4 bi = *reinterpret_cast<const float4 *>(sbias + 0 * UNITS + u);
+                            const float4 bf = *reinterpret_cast<const float4 *>(sbias + 1 * UNITS + u);
+                            const float4 bg = *reinterpret_cast<const float4 *>(sbias + 2 * UNITS + u);
+                            const float4 bo = *reinterpret_cast<const float4 *>(sbias + 3 * UNITS + u);
+                            const float bis[4] = {bi.x, bi.y, bi.z, bi.w}, bfs[4] = {bf.x, bf.y, bf.z, bf.w};
+                            const float bgs[4] = {bg.x, bg.y, bg.z, bg.w}, bos[4] = {bo.x, bo.y, bo.z, bo.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int e = 4 * v + j;
+                                const float i_a = p_hard_sigmoid(__uint_as_float(gi[e]) + bis[j]);
+                                const float f_a = p_hard_sigmoid(__uint_as_float(gf[e]) + bfs[j]);
+                                const float o_a = p_hard_sigmoid(__uint_as_float(go[e]) + bos[j]);
+                                const float g_a = fmaxf(-1.f, fminf(1.f, __uint_as_float(gg[e]) + bgs[j]));
+                                const float c_new = __fmaf_rn(f_a, c[ch * 8 + e], __fmul_rn(i_a, g_a));
+                                c[ch * 8 + e] = c_new;
+                                const float h_new = o_a * p_tanh(c_new);
+                                packed[v] |= (uint32_t(p_quant_h(h_new)) & 0xFFu) << (8 * j);
+                            }
+                        }
+                        if (row_ok) *reinterpret_cast<uint2 *>(hrow + ch * 8) = make_uint2(packed[0], packed[1]);
+                    }
+                    // publish this slice of h_t
+                    ok = warps_barrier(&bar_epi[g], i & 1, lane, abort_flag);
+                    if (ok && q == 2 && lane == 0) {
+                        if (p.trace && blockIdx.x == 0 && g == 0) p.trace[i * 8 + 3] = clock64();
+                        publish(h_ready);
+                        if (p.trace && blockIdx.x == 0 && g == 0) p.trace[i * 8 + 7] = clock64();
+                    }
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int v = 0; v < UNITS / 4; ++v)
+                        *reinterpret_cast<float4 *>(p.c + int64_t(row) * p.H + n0 + 4 * v) =
+                            make_float4(c[4 * v], c[4 * v + 1], c[4 * v + 2], c[4 * v + 3]);
+                }
             }
         }
     } else {
-        const int r0 = part * 64;  // projection columns of this worker
+        const int tile = (blockIdx.x - n_gate) / kPWorkersPerTile;
+        const int r0 = ((blockIdx.x - n_gate) % kPWorkersPerTile) * 64;  // projection columns of this worker
+        const int m0 = tile * 128;
+        unsigned int *h_ready = p.flags + tile;
+        unsigned int *hh_ready = p.flags + p.n_tiles + tile;
         if (warp == 0) {
             // ------------------------------ worker: producer ----------------------------
             if (lane == 0) {
@@ -341,10 +399,11 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                 bool ok = true;
                 for (int i = 0; i < p.T && ok; ++i) {
                     if (i > 0) {
-                        ok = mbar_wait(bar_acc_full, (i - 1) & 1, abort_flag, 48);  // h tile free again
+                        ok = mbar_wait(&bar_acc_full[0], (i - 1) & 1, abort_flag, 48);  // h tile free again
                         if (!ok) break;
                         ok = wait_counter(h_ready, (unsigned)(p.n_slices * i), g_abort, abort_flag, 49);
                         if (!ok) break;
+                        if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 4] = clock64();
                         fence_proxy_async_all();
                     }
                     for (int kb = 0; kb < p.nkb_h; ++kb) {
@@ -360,7 +419,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             constexpr uint32_t kIdesc = make_idesc<kKindI8>(128, 64);
             bool ok = mbar_wait(bar_once, 0, abort_flag, 50);
             for (int i = 0; i < p.T && ok; ++i) {
-                if (i > 0) ok = mbar_wait(bar_acc_empty, (i - 1) & 1, abort_flag, 51);
+                if (i > 0) ok = mbar_wait(&bar_acc_empty[0], (i - 1) & 1, abort_flag, 51);
                 for (int kb = 0; kb < p.nkb_h && ok; ++kb) {
                     ok = mbar_wait(&bar_h[kb], i & 1, abort_flag, 52);
                     if (!ok) break;
@@ -372,7 +431,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         for (int k = 0; k < 4; ++k)
                             tc_mma<kKindI8>(tmem_base, ad + uint64_t(2 * k), bd + uint64_t(2 * k), kIdesc,
                                             (kb | k) != 0 ? 1u : 0u);
-                        if (kb == p.nkb_h - 1) tc_commit(bar_acc_full);
+                        if (kb == p.nkb_h - 1) tc_commit(&bar_acc_full[0]);
                     }
                     __syncwarp();
                 }
@@ -396,15 +455,16 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             __half *orow = p.hh_down + int64_t(row) * kPRank + col0;
             bool ok = true;
             for (int i = 0; i < p.T && ok; ++i) {
-                ok = mbar_wait(bar_acc_full, i & 1, abort_flag, 53);
+                ok = mbar_wait(&bar_acc_full[0], i & 1, abort_flag, 53);
                 if (!ok) break;
+                if (p.trace && int(blockIdx.x) == n_gate && threadIdx.x == 64) p.trace[i * 8 + 5] = clock64();
                 tc_fence_after_sync();
                 uint32_t acc[32];
                 tmem_ld_32x32(t_row, acc);
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_acc_empty);
+                if (lane == 0) mbar_arrive(&bar_acc_empty[0]);
                 if (row_ok) {
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
@@ -419,9 +479,11 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         *reinterpret_cast<uint4 *>(orow + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
-                __threadfence();
-                ok = epi_barrier(bar_epi, i & 1, lane, abort_flag);
-                if (ok && threadIdx.x == 64) atomicAdd(hh_ready, 1u);
+                ok = warps_barrier(&bar_epi[0], i & 1, lane, abort_flag);
+                if (ok && warp == 2 && lane == 0) {
+                    publish(hh_ready);
+                    if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 6] = clock64();
+                }
             }
         }
     }
@@ -454,13 +516,15 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
     }
     PersistDev p;
     p.T = T; p.B = nb; p.b_stride = Bfull; p.H = H; p.reverse = l->reverse;
-    p.n_tiles = (nb + 127) / 128; p.n_slices = H / UNITS; p.nkb_h = H / 128;
+    p.n_tiles = (nb + 127) / 128; p.n_pairs = (p.n_tiles + 1) / 2;
+    p.n_slices = H / UNITS; p.nkb_h = H / 128;
     p.bias = static_cast<const float *>(l->bias_f32);
     p.dn_scale = static_cast<const float *>(l->dn_hh_scale);
     p.c = static_cast<float *>(l->c_f32) + size_t(b0) * H;
     p.h_out = static_cast<int8_t *>(l->h_out_i8) + size_t(b0) * H;
     p.hh_down = hh_down + size_t(b0) * R;
     p.flags = flags;
+    p.trace = g_persist_trace;
 
     CUtensorMap tm_w[4], tm_x, tm_hh, tm_dn, tm_h, tm_h0;
     int rc;
@@ -484,7 +548,7 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
                       nb, H, H, uint64_t(Bfull) * H, 128, 128, true);
     if (rc) return rc;
 
-    const int grid = p.n_tiles * (p.n_slices + kPWorkersPerTile);
+    const int grid = p.n_pairs * p.n_slices + p.n_tiles * kPWorkersPerTile;
     rc = (int)cudaMemsetAsync(flags, 0, sizeof(unsigned int) * (2 * p.n_tiles + 1), stream);
     if (rc) return rc;
     void *args[] = {&tm_w[0], &tm_w[1], &tm_w[2], &tm_w[3], &tm_x, &tm_hh, &tm_dn, &tm_h, &tm_h0, &p};
@@ -492,28 +556,32 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
                                             args, PersistSmem<UNITS>::kDynamic, stream);
 }
 
-// Largest number of 128-row tiles whose CTAs are all co-resident, or 0 when the shape is not
-// covered by the persistent kernel.
+// Largest number of 128-row tiles whose CTAs are all co-resident, or 0 when the device cannot
+// run the kernel cooperatively.
 template <int UNITS>
 int persist_max_tiles(int H) {
-    int dev = 0, sms = 0, per_sm = 0;
+    int dev = 0, sms = 0, per_sm = 0, coop = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
     auto kernel = lstm_persist_kernel<UNITS>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistSmem<UNITS>::kDynamic) != cudaSuccess)
         return 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPThreads, PersistSmem<UNITS>::kDynamic) != cudaSuccess)
         return 0;
-    int coop = 0;
-    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
     if (!coop || per_sm < 1) return 0;
-    return (sms * per_sm) / (H / UNITS + kPWorkersPerTile);
+    const int slots = sms * per_sm, slices = H / UNITS;
+    int tiles = 0;
+    while (((tiles + 2) / 2) * slices + (tiles + 1) * kPWorkersPerTile <= slots) ++tiles;
+    return tiles;
 }
 
 }  // namespace
 }  // namespace fluke_sm100
 
-extern "C" size_t fluke_sm100_lstm_persist_flag_bytes(void) { return 1024; }
+extern "C" void fluke_sm100_lstm_set_trace(void *device_buffer) {
+    fluke_sm100::g_persist_trace = static_cast<long long *>(device_buffer);
+}
 
 // Runs the recurrence of one layer (x_down already computed) with persistent launches. Returns
 // -2 when the shape is not covered (the caller then uses the per-step kernels).
@@ -523,17 +591,17 @@ extern "C" int fluke_sm100_lstm_layer_persistent(const void *layer, const void *
     const fluke_flstm_layer_t *l = static_cast<const fluke_flstm_layer_t *>(layer);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (l->R != kPRank || l->H % 128 || l->H > 128 * kPMaxHKB) return -2;
-    const int units = (l->H % 64 == 0 && l->H / 64 <= 16 && l->H != 768) ? 64 : (l->H % 48 == 0 ? 48 : 0);
-    if (!units) return -2;
-    const int max_tiles = units == 64 ? persist_max_tiles<64>(l->H) : persist_max_tiles<48>(l->H);
+    // hidden units per gate CTA: 24 where H allows it (H = 768 -> 32 slices), else 32
+    const int units = (l->H % 24 == 0) ? 24 : 32;
+    const int max_tiles = units == 24 ? persist_max_tiles<24>(l->H) : persist_max_tiles<32>(l->H);
     if (max_tiles < 1) return -2;
-    const int tiles_per_launch = max_tiles > 64 ? 64 : max_tiles;  // flag buffer holds 2*64+1 words
+    const int tiles_per_launch = max_tiles > 64 ? 64 : max_tiles;  // the counter block holds 2*64+1 words
     for (int b0 = 0; b0 < l->B; b0 += tiles_per_launch * 128) {
         const int nb = l->B - b0 < tiles_per_launch * 128 ? l->B - b0 : tiles_per_launch * 128;
-        const int rc = units == 64
-                           ? persist_launch<64>(l, static_cast<const __half *>(x_down), static_cast<__half *>(hh_down),
+        const int rc = units == 24
+                           ? persist_launch<24>(l, static_cast<const __half *>(x_down), static_cast<__half *>(hh_down),
                                                 static_cast<unsigned int *>(flags), b0, nb, stream)
-                           : persist_launch<48>(l, static_cast<const __half *>(x_down), static_cast<__half *>(hh_down),
+                           : persist_launch<32>(l, static_cast<const __half *>(x_down), static_cast<__half *>(hh_down),
                                                 static_cast<unsigned int *>(flags), b0, nb, stream);
         if (rc) return rc;
     }

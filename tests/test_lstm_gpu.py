@@ -180,4 +180,7 @@ def test_layer_config_size_properties(lstm_mode):
     A = torch.cat([torch.zeros(B, R, dtype=torch.float16, device=DEV), xd], dim=1).contiguous()
     c3 = torch.zeros(B, H, device=DEV)
     h3 = ops.factored_lstm_step_i8(A, layer.w_up, layer.bias, c3)
-    assert torch.equal(h3, fwd[0])
+    d = (h3.int() - fwd[0].int()).abs()   # the persistent kernel uses the fast-exp tanh: rare one-code ties
+    assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 1e-3
+    if lstm_mode == "per_step":
+        assert torch.equal(h3, fwd[0])
