@@ -58,6 +58,11 @@ int fluke_sm100_flstm_step(const void *scratch, const void *ih_t, void *cell, vo
                            int batch_size, int hidden_dim, void *stream);
 int fluke_sm100_fp8_unshuffle(void *dst_nk, const void *src, int N, int K, void *stream);
 
+/* tcgen05.mma issue-rate probe: n_ctas CTAs each time `iters` back-to-back MMAs of shape
+ * 128 x n x 32 bytes (kind 0 int8, 1 e4m3, 2 f16) on shared-memory-resident operands and write
+ * their SM-clock cycle counts to cycles_dev[0 .. n_ctas) (device, int64). */
+int fluke_sm100_mma_peak(int kind, int n, int iters, void *cycles_dev, int n_ctas, void *stream);
+
 /* ---- tcgen05 GEMM family ---------------------------------------------------------------- */
 
 enum fluke_sm100_kind {

@@ -6,3 +6,4 @@
 #include "lstm_sm100.cu"
 #include "lstm_persist_sm100.cu"
 #include "lstm_noalloc_sm100.cu"
+#include "mma_peak_sm100.cu"

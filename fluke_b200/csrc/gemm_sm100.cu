@@ -1,18 +1,24 @@
 // gemm_sm100.cu -- the tcgen05 GEMM family of the quantized transformer path on sm_100a.
 //
-// One persistent, warp-specialised kernel template computes out = epilogue(A @ B^T) for
-// K-major 8-bit operands (int8 -> int32 via kind::i8, e4m3 -> f32 via kind::f8f6f4):
+// One persistent, warp-specialised, WEIGHT-STATIONARY kernel template computes
+// out = epilogue(A @ B^T) for K-major 8-bit operands (int8 -> int32 via kind::i8,
+// e4m3 -> f32 via kind::f8f6f4). A CTA owns one N tile of the weight for its whole life: the
+// tile (all of K, up to 128 KB) is TMA-loaded into shared memory once, and the CTA then streams
+// the M tiles assigned to it, so per output tile only the 128 x K activation block crosses
+// L2 -> SM (the activations are what is large; the weights of this path are at most 2 MB).
 //
-//   warp 0      TMA producer: 128-byte-swizzled A and B tiles into a ring of smem stages
-//   warp 1      MMA issuer:   tcgen05.mma 128 x BN x 32B from shared-memory descriptors into
-//               one of two accumulator buffers in tensor memory
-//   warps 2-9   epilogue:     two warps per TMEM lane quadrant, each owning half of the tile's
+//   warp 0      TMA producer: the resident weight tile once, then 128-byte-swizzled A blocks
+//               into a ring of shared-memory stages
+//   warp 1      MMA issuer: tcgen05.mma 128 x BN x 32B from shared-memory descriptors into one
+//               of two accumulator buffers in tensor memory
+//   warps 2-9   epilogue: two warps per TMEM lane quadrant, each owning half of the tile's
 //               columns: tcgen05.ld (thread = output row), dequant / rotary / SiLU in
 //               registers, f16 pack, swizzled smem staging, TMA tile store
 //
 // The two accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1; no
 // accumulator or f16 intermediate ever reaches HBM. The rotary tables of a tile's 128 rows are
-// staged once per tile in shared memory (coalesced loads, swizzled rows) and read per head.
+// staged once per tile in shared memory (coalesced loads, swizzled rows); the weight scales of
+// the CTA's N tile are staged once per launch.
 // It replaces TensorOpGemmI8 (cute/ampere/gemm/gemm_i8_quant.py:344-757), TensorOpGemmI8Rotary
 // (cute/ampere/rotary/gemm_i8_rotary.py:151-472) and TensorOpDualGemmI8Silu
 // (cute/ampere/dual_gemm_silu/dual_gemm_i8_silu.py:150-523) of the reference, and follows
@@ -36,10 +42,12 @@ constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueWarps = 8;
 constexpr int kStageRows = 32;        // rows per epilogue warp
 constexpr int kStagingBytes = kStageRows * 128;
+constexpr int kWeightBytes = 128 * 1024;  // resident weight tile: BN_MMA rows x K bytes
 
 struct GemmDev {
     int M, N, K;
     int num_m_tiles, num_n_tiles, num_k_blocks;
+    int ctas_per_n;          // CTAs that share one N tile (they split the M tiles)
     const float *scale_a;
     float const_scale_a;
     const float *scale_b;
@@ -49,23 +57,22 @@ struct GemmDev {
     int seqlen;
     int qk_cols;
     int a_plane;  // plane of the 3-D A tensor map this launch reads
-    long long *trace;  // optional: cycle counters of CTA 0 (development aid)
 };
 
-static long long *g_gemm_trace = nullptr;
 
 template <int EPI, int BN_MMA, int STAGES>
 struct SmemLayout {
     static constexpr bool kRotary = (EPI == FLUKE_SM100_EPI_ROTARY);
-    static constexpr int kStagingBufs = kRotary ? 1 : 2;   // per epilogue warp
+    static constexpr int kMaxKBlocks = kWeightBytes / (BN_MMA * kBlockKBytes);  // 4 (BN 256) or 8 (BN 128)
     static constexpr int kABytes = kBlockM * kBlockKBytes;
-    static constexpr int kBBytes = BN_MMA * kBlockKBytes;
-    static constexpr int kOffA = 0;
-    static constexpr int kOffB = kOffA + STAGES * kABytes;
-    static constexpr int kOffStaging = kOffB + STAGES * kBBytes;
-    static constexpr int kOffTables = kOffStaging + kEpilogueWarps * kStagingBufs * kStagingBytes;
-    static constexpr int kOffBars = kOffTables + (kRotary ? 4 * 8192 : 0);  // per quadrant: sin 4 KB | cos 4 KB
-    static constexpr int kNumBars = 2 * STAGES + 4 + 8;
+    static constexpr int kBBytes = BN_MMA * kBlockKBytes;   // one K block of the weight tile
+    static constexpr int kOffW = 0;
+    static constexpr int kOffA = kWeightBytes;
+    static constexpr int kOffStaging = kOffA + STAGES * kABytes;
+    static constexpr int kOffTables = kOffStaging + kEpilogueWarps * kStagingBytes;
+    static constexpr int kOffScaleB = kOffTables + (kRotary ? 4 * 8192 : 0);  // per quadrant: sin 4 KB | cos 4 KB
+    static constexpr int kOffBars = kOffScaleB + (EPI == FLUKE_SM100_EPI_SILU ? 0 : BN_MMA * 4);
+    static constexpr int kNumBars = 2 * STAGES + 5 + 8;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kTotal = kOffMisc + 16;
     static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
@@ -106,6 +113,11 @@ __device__ __forceinline__ bool pair_barrier(uint64_t *bar, uint32_t parity, int
     return mbar_wait(bar, parity, abort_flag, 5);
 }
 
+__device__ __forceinline__ void ld4(const float *p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4 *>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+
 template <int KIND, int EPI, int BN_MMA, int STAGES>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -115,7 +127,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     constexpr bool kDual = (EPI == FLUKE_SM100_EPI_SILU);
     constexpr int BN_OUT = kDual ? BN_MMA / 2 : BN_MMA;  // output columns per tile
     constexpr int kWarpCols = BN_OUT / 2;                // output columns per epilogue warp
-    constexpr uint32_t kStageTxBytes = L::kABytes + L::kBBytes;
     constexpr uint32_t kTmemCols = 2 * BN_MMA;  // two accumulator buffers (256 or 512)
     constexpr uint32_t kIdesc = make_idesc<KIND>(kBlockM, BN_MMA);
 
@@ -127,13 +138,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     uint64_t *empty_bar = bars + STAGES;
     uint64_t *tfull_bar = bars + 2 * STAGES;
     uint64_t *tempty_bar = bars + 2 * STAGES + 2;
-    uint64_t *tab_full_bar = bars + 2 * STAGES + 4;   // [4] tables of the quadrant are staged
-    uint64_t *tab_empty_bar = bars + 2 * STAGES + 8;  // [4] both warps are done reading them
+    uint64_t *w_bar = bars + 2 * STAGES + 4;          // resident weight tile loaded
+    uint64_t *tab_full_bar = bars + 2 * STAGES + 5;   // [4] tables of the quadrant are staged
+    uint64_t *tab_empty_bar = bars + 2 * STAGES + 9;  // [4] both warps are done reading them
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kOffMisc + 4);
+    float *sbs = reinterpret_cast<float *>(smem + L::kOffScaleB);  // weight scales of this N tile
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int n_tile = blockIdx.x % p.num_n_tiles;
+    const int m_first = blockIdx.x / p.num_n_tiles;
+    const int n0 = n_tile * BN_OUT;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -144,6 +160,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             mbar_init(&tfull_bar[s], 1);
             mbar_init(&tempty_bar[s], kEpilogueWarps);
         }
+        mbar_init(w_bar, 1);
         for (int s = 0; s < 4; ++s) {
             mbar_init(&tab_full_bar[s], 2);
             mbar_init(&tab_empty_bar[s], 2);
@@ -156,38 +173,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         tma_prefetch_desc(&tm_out);
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    if (warp >= kEpilogueWarp0) {
+        // weight scales of the tile's columns (zeros past N), read by every epilogue thread
+        if constexpr (EPI != FLUKE_SM100_EPI_RAW && EPI != FLUKE_SM100_EPI_SILU) {
+            for (int j = threadIdx.x - 64; j < BN_MMA; j += kEpilogueWarps * 32) {
+                float v;
+                if (kDual) {
+                    const int col = n0 + (j % BN_OUT);
+                    v = col < p.N ? __ldg((j < BN_OUT ? p.scale_b : p.scale_b2) + col) : 0.f;
+                } else {
+                    v = n0 + j < p.N ? __ldg(p.scale_b + n0 + j) : 0.f;
+                }
+                sbs[j] = v;
+            }
+        }
+    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
-
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w_bar, uint32_t(p.num_k_blocks) * L::kBBytes);
+            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                uint8_t *sb = smem + L::kOffW + kb * L::kBBytes;
+                if constexpr (kDual) {
+                    tma_load_2d(sb, &tm_b, w_bar, kb * kBlockKBytes, n0);
+                    tma_load_2d(sb + L::kBBytes / 2, &tm_b2, w_bar, kb * kBlockKBytes, n0);
+                } else {
+                    tma_load_2d(sb, &tm_b, w_bar, kb * kBlockKBytes, n0);
+                }
+            }
+        }
+        __syncwarp();
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile / p.num_n_tiles) * kBlockM;
-            const int n0 = (tile % p.num_n_tiles) * BN_OUT;
+        for (int mt = m_first; mt < p.num_m_tiles && ok; mt += p.ctas_per_n) {
+            const int m0 = mt * kBlockM;
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                const long long tw0 = clock64();
                 ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, 1);
                 if (!ok) break;
-                if (p.trace && blockIdx.x == 0 && lane == 0) p.trace[0] += clock64() - tw0;
                 if (lane == 0) {
-                    mbar_arrive_expect_tx(&full_bar[stage], kStageTxBytes);
-                    uint8_t *sa = smem + L::kOffA + stage * L::kABytes;
-                    uint8_t *sb = smem + L::kOffB + stage * L::kBBytes;
-                    tma_load_3d(sa, &tm_a, &full_bar[stage], kb * kBlockKBytes, m0, p.a_plane);
-                    if constexpr (kDual) {
-                        tma_load_2d(sb, &tm_b, &full_bar[stage], kb * kBlockKBytes, n0);
-                        tma_load_2d(sb + L::kBBytes / 2, &tm_b2, &full_bar[stage],
-                                    kb * kBlockKBytes, n0);
-                    } else {
-                        tma_load_2d(sb, &tm_b, &full_bar[stage], kb * kBlockKBytes, n0);
-                    }
+                    mbar_arrive_expect_tx(&full_bar[stage], L::kABytes);
+                    tma_load_3d(smem + L::kOffA + stage * L::kABytes, &tm_a, &full_bar[stage],
+                                kb * kBlockKBytes, m0, p.a_plane);
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -204,27 +236,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         int stage = 0;
         uint32_t phase = 0;
         int local = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        bool ok = mbar_wait(w_bar, 0, abort_flag, 6);
+        for (int mt = m_first; mt < p.num_m_tiles && ok; mt += p.ctas_per_n, ++local) {
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
-            const long long tw1 = clock64();
             ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, 2);
             if (!ok) break;
-            if (p.trace && blockIdx.x == 0 && lane == 0) p.trace[1] += clock64() - tw1;
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + acc * BN_MMA;
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                const long long tw2 = clock64();
                 ok = mbar_wait(&full_bar[stage], phase, abort_flag, 3);
                 if (!ok) break;
-                if (p.trace && blockIdx.x == 0 && lane == 0) p.trace[2] += clock64() - tw2;
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint64_t adesc =
                         make_smem_desc_sw128(smem_u32(smem + L::kOffA + stage * L::kABytes));
                     const uint64_t bdesc =
-                        make_smem_desc_sw128(smem_u32(smem + L::kOffB + stage * L::kBBytes));
+                        make_smem_desc_sw128(smem_u32(smem + L::kOffW + kb * L::kBBytes));
 #pragma unroll
                     for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
                         tc_mma<KIND>(d_tmem, adesc + uint64_t(k * (kUmmaKBytes >> 4)),
@@ -242,16 +270,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // ------------------------------ epilogue ----------------------------------
         const int q = warp & 3;                           // TMEM lane quadrant this warp may read
         const int ch = (warp - kEpilogueWarp0) >> 2;      // which half of the tile's columns
-        const int ew = warp - kEpilogueWarp0;
-        uint8_t *staging0 = smem + L::kOffStaging + ew * L::kStagingBufs * kStagingBytes;
+        uint8_t *staging = smem + L::kOffStaging + (warp - kEpilogueWarp0) * kStagingBytes;
         uint8_t *tables = smem + L::kOffTables + q * 8192;  // ROTARY only
+        const bool rotate = (EPI == FLUKE_SM100_EPI_ROTARY) && n0 < p.qk_cols;
         int local = 0;
-        int store_idx = 0;
         uint32_t tab_phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-            const int m0 = (tile / p.num_n_tiles) * kBlockM;
-            const int n0 = (tile % p.num_n_tiles) * BN_OUT;
+        for (int mt = m_first; mt < p.num_m_tiles && ok; mt += p.ctas_per_n, ++local) {
+            const int m0 = mt * kBlockM;
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row = m0 + q * 32 + lane;
@@ -264,9 +290,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
             // Rotary tables of the quadrant's 32 rows, staged once per tile: warp ch = 0 copies
             // the sin rows, ch = 1 the cos rows (coalesced 16-byte loads, swizzled 128-byte rows).
-            bool rotate = false;
             if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
-                rotate = n0 < p.qk_cols;
                 if (rotate) {
                     const float *src = ch == 0 ? p.sin_tab : p.cos_tab;
 #pragma unroll
@@ -283,11 +307,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
             }
 
-            const long long tw3 = clock64();
             ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 4);
             if (!ok) break;
-            const long long tw4 = clock64();
-            if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) { p.trace[3] += tw4 - tw3; p.trace[7] += 1; }
             tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA;
 
@@ -310,68 +331,73 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         uint32_t g[32], u[32];
                         tmem_ld_32x32(t_row + c0 + half * 32, g);
                         tmem_ld_32x32(t_row + BN_OUT + c0 + half * 32, u);
-                        tmem_ld_wait();
-                        const float4 *sg4 =
-                            reinterpret_cast<const float4 *>(p.scale_b + n0 + c0 + half * 32);
-                        const float4 *su4 =
-                            reinterpret_cast<const float4 *>(p.scale_b2 + n0 + c0 + half * 32);
+                        float sg[32], su[32];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            const float4 sg = __ldg(sg4 + i), su = __ldg(su4 + i);
-                            const float sgv[4] = {sg.x, sg.y, sg.z, sg.w};
-                            const float suv[4] = {su.x, su.y, su.z, su.w};
-                            float o[4];
+                            // weight scales through L1 (the same address in every lane); N % 128 == 0 here
+                            const float4 a4 = __ldg(reinterpret_cast<const float4 *>(p.scale_b + n0 + c0 + half * 32) + i);
+                            const float4 b4 = __ldg(reinterpret_cast<const float4 *>(p.scale_b2 + n0 + c0 + half * 32) + i);
+                            sg[4 * i] = a4.x; sg[4 * i + 1] = a4.y; sg[4 * i + 2] = a4.z; sg[4 * i + 3] = a4.w;
+                            su[4 * i] = b4.x; su[4 * i + 1] = b4.y; su[4 * i + 2] = b4.z; su[4 * i + 3] = b4.w;
+                        }
+                        tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float gate = (acc_to_float<KIND>(g[4 * i + j]) * sa) * sgv[j];
-                                const float up = (acc_to_float<KIND>(u[4 * i + j]) * sa) * suv[j];
+                        for (int i = 0; i < 16; ++i) {
+                            float o[2];
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const int e = 2 * i + j;
+                                const float gate = (acc_to_float<KIND>(g[e]) * sa) * sg[e];
+                                const float up = (acc_to_float<KIND>(u[e]) * sa) * su[e];
                                 const float sig = 0.5f * tanh_approx(0.5f * gate) + 0.5f;
                                 o[j] = gate * sig * up;
                             }
-                            outw[half * 16 + 2 * i] = pack_half2(o[0], o[1]);
-                            outw[half * 16 + 2 * i + 1] = pack_half2(o[2], o[3]);
+                            outw[half * 16 + i] = pack_half2(o[0], o[1]);
                         }
                     }
                 } else if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
-                    // One head: pairs (i, i+32). Two passes of 16 pairs keep the register count down.
+                    // One head: pairs (i, i+32). Two passes of 16 pairs; every load of a pass is
+                    // issued before its first use.
 #pragma unroll
                     for (int sub = 0; sub < 2; ++sub) {
                         uint32_t lo[16], hi[16];
                         tmem_ld_32x16(t_row + c0 + sub * 16, lo);
                         tmem_ld_32x16(t_row + c0 + 32 + sub * 16, hi);
-                        tmem_ld_wait();
-                        const float4 *sb_lo = reinterpret_cast<const float4 *>(p.scale_b + n0 + c0 + sub * 16);
-                        const float4 *sb_hi = sb_lo + 8;
+                        float bl[16], bh[16], sn[16], cs[16];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const float4 bl = __ldg(sb_lo + i), bh = __ldg(sb_hi + i);
-                            const float blv[4] = {bl.x, bl.y, bl.z, bl.w};
-                            const float bhv[4] = {bh.x, bh.y, bh.z, bh.w};
-                            float snv[4] = {0.f, 0.f, 0.f, 0.f}, csv[4] = {1.f, 1.f, 1.f, 1.f};
+                            float t4[4];
+                            ld4(sbs + c0 + sub * 16 + 4 * i, t4);
+                            bl[4 * i] = t4[0]; bl[4 * i + 1] = t4[1]; bl[4 * i + 2] = t4[2]; bl[4 * i + 3] = t4[3];
+                            ld4(sbs + c0 + 32 + sub * 16 + 4 * i, t4);
+                            bh[4 * i] = t4[0]; bh[4 * i + 1] = t4[1]; bh[4 * i + 2] = t4[2]; bh[4 * i + 3] = t4[3];
                             if (rotate) {
-                                const float4 s4 = *reinterpret_cast<const float4 *>(tables + sw128_offset(lane, sub * 4 + i));
-                                const float4 c4 = *reinterpret_cast<const float4 *>(tables + 4096 + sw128_offset(lane, sub * 4 + i));
-                                snv[0] = s4.x; snv[1] = s4.y; snv[2] = s4.z; snv[3] = s4.w;
-                                csv[0] = c4.x; csv[1] = c4.y; csv[2] = c4.z; csv[3] = c4.w;
+                                ld4(reinterpret_cast<const float *>(tables + sw128_offset(lane, sub * 4 + i)), t4);
+                                sn[4 * i] = t4[0]; sn[4 * i + 1] = t4[1]; sn[4 * i + 2] = t4[2]; sn[4 * i + 3] = t4[3];
+                                ld4(reinterpret_cast<const float *>(tables + 4096 + sw128_offset(lane, sub * 4 + i)), t4);
+                                cs[4 * i] = t4[0]; cs[4 * i + 1] = t4[1]; cs[4 * i + 2] = t4[2]; cs[4 * i + 3] = t4[3];
                             }
-                            float o_lo[4], o_hi[4];
+                        }
+                        tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float x0 = (acc_to_float<KIND>(lo[4 * i + j]) * sa) * blv[j];
-                                const float x1 = (acc_to_float<KIND>(hi[4 * i + j]) * sa) * bhv[j];
+                        for (int i = 0; i < 8; ++i) {
+                            float o_lo[2], o_hi[2];
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const int e = 2 * i + j;
+                                const float x0 = (acc_to_float<KIND>(lo[e]) * sa) * bl[e];
+                                const float x1 = (acc_to_float<KIND>(hi[e]) * sa) * bh[e];
                                 if (rotate) {
                                     // fixed operation order (no compiler-chosen contraction)
-                                    o_lo[j] = __fmaf_rn(x0, csv[j], -__fmul_rn(x1, snv[j]));
-                                    o_hi[j] = __fmaf_rn(x0, snv[j], __fmul_rn(x1, csv[j]));
+                                    o_lo[j] = __fmaf_rn(x0, cs[e], -__fmul_rn(x1, sn[e]));
+                                    o_hi[j] = __fmaf_rn(x0, sn[e], __fmul_rn(x1, cs[e]));
                                 } else {
                                     o_lo[j] = x0;
                                     o_hi[j] = x1;
                                 }
                             }
-                            outw[sub * 8 + 2 * i] = pack_half2(o_lo[0], o_lo[1]);
-                            outw[sub * 8 + 2 * i + 1] = pack_half2(o_lo[2], o_lo[3]);
-                            outw[16 + sub * 8 + 2 * i] = pack_half2(o_hi[0], o_hi[1]);
-                            outw[16 + sub * 8 + 2 * i + 1] = pack_half2(o_hi[2], o_hi[3]);
+                            outw[sub * 8 + i] = pack_half2(o_lo[0], o_lo[1]);
+                            outw[16 + sub * 8 + i] = pack_half2(o_hi[0], o_hi[1]);
                         }
                     }
                 } else {
@@ -380,21 +406,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     for (int half = 0; half < 2; ++half) {
                         uint32_t a[32];
                         tmem_ld_32x32(t_row + c0 + half * 32, a);
-                        tmem_ld_wait();
-                        const float4 *sb4 = reinterpret_cast<const float4 *>(p.scale_b + n0 + c0 + half * 32);
+                        float bv[32];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            const float4 b = __ldg(sb4 + i);
-                            const float bv[4] = {b.x, b.y, b.z, b.w};
-                            float o[4];
+                            float t4[4];
+                            ld4(sbs + c0 + half * 32 + 4 * i, t4);
+                            bv[4 * i] = t4[0]; bv[4 * i + 1] = t4[1]; bv[4 * i + 2] = t4[2]; bv[4 * i + 3] = t4[3];
+                        }
+                        tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float v = acc_to_float<KIND>(a[4 * i + j]);
-                                if constexpr (EPI == FLUKE_SM100_EPI_DEQUANT) o[j] = v * (sa * bv[j]);
-                                else o[j] = (v * sa) * bv[j];
+                        for (int i = 0; i < 16; ++i) {
+                            float o[2];
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                const float v = acc_to_float<KIND>(a[2 * i + j]);
+                                if constexpr (EPI == FLUKE_SM100_EPI_DEQUANT) o[j] = v * (sa * bv[2 * i + j]);
+                                else o[j] = (v * sa) * bv[2 * i + j];
                             }
-                            outw[half * 16 + 2 * i] = pack_half2(o[0], o[1]);
-                            outw[half * 16 + 2 * i + 1] = pack_half2(o[2], o[3]);
+                            outw[half * 16 + i] = pack_half2(o[0], o[1]);
                         }
                     }
                 }
@@ -408,11 +437,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
 
                 if (!chunk_ok) continue;
-                uint8_t *staging = staging0 + (store_idx % L::kStagingBufs) * kStagingBytes;
-                const long long tw5 = clock64();
-                if (lane == 0) tma_store_wait_read<L::kStagingBufs - 1>();
+                if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
-                if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) p.trace[4] += clock64() - tw5;
                 stage_row(staging, lane, outw);
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -420,9 +446,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     tma_store_2d(&tm_out, staging, n0 + c0, m0 + q * 32);
                     tma_store_commit();
                 }
-                ++store_idx;
             }
-            if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) p.trace[5] += clock64() - tw4;
             if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
                 if (rotate) {
                     // both warps of the quadrant are done with the tables of this tile
@@ -524,10 +548,16 @@ int plan_build(const fluke_sm100_gemm_t *g, int a_planes, GemmPlan *plan) {
     p.seqlen = g->seqlen > 0 ? g->seqlen : 1;
     p.qk_cols = g->qk_cols;
     p.a_plane = 0;
-    p.trace = g_gemm_trace;
-    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    // weight-stationary schedule: every N tile gets the same number of CTAs, which split the
+    // M tiles between them
     const int sms = device_sm_count();
-    plan->grid = tiles < sms ? tiles : sms;
+    if (p.num_n_tiles > sms || p.num_k_blocks > SmemLayout<EPI, BN_MMA, STAGES>::kMaxKBlocks)
+        return (int)cudaErrorInvalidValue;  // N tile count / K beyond what one resident tile covers
+    int per_n = sms / p.num_n_tiles;
+    if (per_n > p.num_m_tiles) per_n = p.num_m_tiles;
+    if (per_n < 1) per_n = 1;
+    p.ctas_per_n = per_n;
+    plan->grid = p.num_m_tiles > 0 ? per_n * p.num_n_tiles : 0;
     return 0;
 }
 
@@ -554,10 +584,12 @@ int launch(const fluke_sm100_gemm_t *g, cudaStream_t stream) {
     return plan_launch<KIND, EPI, BN_MMA, STAGES>(plan, 0, stream);
 }
 
-// Tile shapes: 128 x 128 with a 4-deep ring for the plain GEMMs; 128 x 256 (one UMMA of
-// N = 256 per K step) with a 3-deep ring for the two fused transformer kernels.
+// Tile shapes: 128 x 128 (K up to 1024 resident) for the plain GEMMs; 128 x 256 (one UMMA of
+// N = 256 per K step, K up to 512 resident) for the two fused transformer kernels. The last
+// number is the depth of the ring of 16 KB activation stages that fits beside the resident
+// weight tile, the store staging and (rotary) the tables.
 constexpr int kPlainBN = 128, kPlainStages = 4;
-constexpr int kFusedBN = 256, kFusedStages = 3;
+constexpr int kFusedBN = 256, kFusedStages = 2, kSiluStages = 4;
 
 template <int KIND>
 int dispatch(const fluke_sm100_gemm_t *g, cudaStream_t s) {
@@ -571,7 +603,7 @@ int dispatch(const fluke_sm100_gemm_t *g, cudaStream_t s) {
         case FLUKE_SM100_EPI_ROTARY:
             return launch<KIND, FLUKE_SM100_EPI_ROTARY, kFusedBN, kFusedStages>(g, s);
         case FLUKE_SM100_EPI_SILU:
-            return launch<KIND, FLUKE_SM100_EPI_SILU, kFusedBN, kFusedStages>(g, s);
+            return launch<KIND, FLUKE_SM100_EPI_SILU, kFusedBN, kSiluStages>(g, s);
         default:
             return (int)cudaErrorInvalidValue;
     }
@@ -585,6 +617,9 @@ int dispatch(const fluke_sm100_gemm_t *g, cudaStream_t s) {
 extern "C" int fluke_sm100_gemm(const fluke_sm100_gemm_t *g, void *stream) {
     using namespace fluke_sm100;
     if (!g || g->M < 0 || g->N <= 0 || g->K <= 0) return (int)cudaErrorInvalidValue;
+    // the weight tile of a CTA stays resident: K <= 1024 bytes (plain) / 512 bytes (fused kernels)
+    if (g->K > ((g->epilogue == FLUKE_SM100_EPI_ROTARY || g->epilogue == FLUKE_SM100_EPI_SILU) ? 512 : 1024))
+        return (int)cudaErrorInvalidValue;
     if (g->K % 16 != 0 || g->N % 64 != 0) return (int)cudaErrorInvalidValue;
     if (g->epilogue == FLUKE_SM100_EPI_ROTARY && (g->qk_cols % 256 != 0 || g->N % 256 != 0))
         return (int)cudaErrorInvalidValue;
@@ -593,10 +628,6 @@ extern "C" int fluke_sm100_gemm(const fluke_sm100_gemm_t *g, void *stream) {
     if (g->kind == FLUKE_SM100_KIND_I8) return dispatch<kKindI8>(g, s);
     if (g->kind == FLUKE_SM100_KIND_F8) return dispatch<kKindF8>(g, s);
     return (int)cudaErrorInvalidValue;
-}
-
-extern "C" void fluke_sm100_gemm_set_trace(void *device_buffer) {
-    fluke_sm100::g_gemm_trace = static_cast<long long *>(device_buffer);
 }
 
 extern "C" int fluke_sm100_compute_capability(int device_index) {
