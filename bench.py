@@ -156,6 +156,37 @@ def time_rotating(calls, iters, torch):
     return e0.elapsed_time(e1) / (iters * len(calls))
 
 
+def measure_tensor_peaks(torch):
+    """tcgen05.mma issue-rate probe on every SM (operands resident in shared memory, no global
+    traffic): the measured tensor-pipe ceiling for int8 / e4m3 / f16 at the SM clock of the run.
+    MEASURED_PEAKS.json only has bf16 through cuBLAS, so the int8/fp8 fractions of the GEMM-class
+    kernels are quoted against these."""
+    import ctypes
+    from fluke_b200 import lib as flib
+    L = flib.load()
+    fn = L.fluke_sm100_mma_peak
+    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    cyc = torch.zeros(sms, dtype=torch.int64, device="cuda")
+    out = {}
+    iters = 16384
+    for kind, name, kelems in ((0, "int8", 32), (1, "e4m3", 32), (2, "f16", 16)):
+        fn(kind, 256, iters, cyc.data_ptr(), sms, None)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = fn(kind, 256, iters, cyc.data_ptr(), sms, None)
+        e1.record()
+        torch.cuda.synchronize()
+        if rc != 0:
+            continue
+        ops = 2.0 * 128 * 256 * kelems * iters * sms
+        out[name] = {"TOPs": round(ops / e0.elapsed_time(e1) / 1e9, 1),
+                     "ops_per_clk_per_sm": round(2.0 * 128 * 256 * kelems * iters / cyc.float().mean().item(), 1)}
+    return out
+
+
 def bench_ops(torch, peaks):
     """Configs 1-4 of the path; each entry reports time, achieved GB/s or TOP/s and the fraction
     of the measured HBM copy bandwidth (frac_hbm) that the algorithmic bytes imply."""
@@ -318,8 +349,7 @@ def run_ours(args):
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) / reps * 1e3   # microseconds
         us_layer, us_xdown = time_mask(7), time_mask(1)
-        per_kernel = {"layer_total": us_layer, "x_down_gemm": us_xdown, "lstm_persist_kernel": us_layer - us_xdown,
-                      "per_step_lstm_step_kernel": time_mask(4) / T, "per_step_down_proj_gemm": time_mask(2) / T}
+        per_kernel = {"layer_total": us_layer, "x_down_gemm": us_xdown, "lstm_persist_kernel": us_layer - us_xdown}
         flops = T * (2.0 * B * (2 * R) * (4 * H) + 2.0 * B * R * H)   # f16 gate contraction + int8 hh projection
         achieved = flops / (per_kernel["lstm_persist_kernel"] * 1e-6) / 1e12
         roofline = {"kernel": "lstm_persist_kernel", "bound": "tensor", "achieved": round(achieved, 2),
@@ -327,7 +357,8 @@ def run_ours(args):
                     "peak_source": f"{peaks['source']} bf16 GEMM, sustained", "traffic": None,
                     "flops_per_launch": flops, "us_per_launch": {k: round(v, 3) for k, v in per_kernel.items()}}
         cpu_v, cores, sample = cpu_lstm_sample()
-        ops_res = bench_ops(torch, peaks) if world == 1 or True else {}
+        ops_res = bench_ops(torch, peaks)
+        tensor_peaks = measure_tensor_peaks(torch)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f16",
@@ -342,7 +373,7 @@ def run_ours(args):
             "clocks": clocks, "roofline": roofline,
             "cpu_baseline": {"value": cpu_v, "unit": "chunk-timesteps/s (per layer)", "cores": cores, "kind": "port",
                              "sample": sample},
-            "ops": ops_res,
+            "ops": ops_res, "tensor_peaks_measured": tensor_peaks,
         }
     if world > 1:
         dist.barrier()

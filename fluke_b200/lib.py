@@ -78,6 +78,7 @@ SIGNATURES = {
     "fluke_factored_lstm_layer_i8_noalloc_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t)]),
     # internal status word (bounded device waits)
     "fluke_sm100_read_status": (I, [ctypes.POINTER(ctypes.c_uint), I]),
+    "fluke_sm100_mma_peak": (I, [I, I, I, P, I, P]),
 }
 for _n, _a in VOID_SIGNATURES.items():
     SIGNATURES[_n] = (None, _a)
