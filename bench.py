@@ -115,8 +115,7 @@ def cpu_lstm_sample(seconds_target=15.0):
     import torch
     from fluke_b200 import prep
     from oracle import port
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    cores = port.set_threads(os.cpu_count() or 1)   # torchrun exports OMP_NUM_THREADS=1
     g = torch.Generator().manual_seed(42)
     H, R = HIDDEN, RANK
 

@@ -59,6 +59,14 @@ def _call(name, *args):
     fn(*conv)
 
 
+def set_threads(n):
+    """OpenMP threads used by the parallel oracle loops; returns the count in effect."""
+    fn = lib().orc_set_threads
+    fn.restype = I
+    fn.argtypes = [I]
+    return fn(int(n))
+
+
 def set_fma_modes(sumsq=1, resadd=1, rot_lo=1, rot_hi=1, gate=1, cell=2):
     _call("orc_set_fma_modes", sumsq, resadd, rot_lo, rot_hi, gate, cell)
 
