@@ -7,18 +7,25 @@
 // the M tiles assigned to it, so per output tile only the 128 x K activation block crosses
 // L2 -> SM (the activations are what is large; the weights of this path are at most 2 MB).
 //
-//   warp 0      TMA producer: the resident weight tile once, then 128-byte-swizzled A blocks
-//               into a ring of shared-memory stages
-//   warp 1      MMA issuer: tcgen05.mma 128 x BN x 32B from shared-memory descriptors into one
-//               of two accumulator buffers in tensor memory
-//   warps 2-9   epilogue: two warps per TMEM lane quadrant, each owning half of the tile's
-//               columns: tcgen05.ld (thread = output row), dequant / rotary / SiLU in
-//               registers, f16 pack, swizzled smem staging, TMA tile store
+// 384 threads in three warpgroups; after set-up the first gives most of its registers to the
+// other two (setmaxnreg):
+//
+//   warp 0      TMA producer (one thread): the resident weight tile once, then
+//               128-byte-swizzled 128 x 128-byte A blocks into a ring of four stages; it also
+//               pulls the A tile three steps ahead into L2
+//   warp 1      MMA issuer (one thread): tcgen05.mma 128 x BN x 32B from shared-memory
+//               descriptors into one of two accumulator buffers in tensor memory
+//   warps 2-3   idle
+//   warps 4-11  epilogue: two warps per TMEM lane quadrant, each owning half of the tile's
+//               columns: tcgen05.ld, dequant / rotary / SiLU in packed f32x2 arithmetic, f16
+//               pack, swizzled smem staging, TMA tile store
 //
 // The two accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1; no
-// accumulator or f16 intermediate ever reaches HBM. The rotary tables of a tile's 128 rows are
-// staged once per tile in shared memory (coalesced loads, swizzled rows); the weight scales of
-// the CTA's N tile are staged once per launch.
+// accumulator or f16 intermediate ever reaches HBM. Per-column and per-position factors live in
+// registers wherever the data layout allows it: the SiLU and dequant epilogues read tensor
+// memory in the 16-lane x 256-bit shape, in which a thread keeps the same 16 columns for the
+// whole kernel (their weight scales are loaded once); the rotary epilogue keeps thread = row
+// and, with tiles aligned to the sequences, holds the row's sin/cos values across tiles.
 // It replaces TensorOpGemmI8 (cute/ampere/gemm/gemm_i8_quant.py:344-757), TensorOpGemmI8Rotary
 // (cute/ampere/rotary/gemm_i8_rotary.py:151-472) and TensorOpDualGemmI8Silu
 // (cute/ampere/dual_gemm_silu/dual_gemm_i8_silu.py:150-523) of the reference, and follows
@@ -35,10 +42,13 @@ namespace fluke_sm100 {
 namespace {
 
 constexpr int kBlockM = 128;          // rows per tile = TMEM lanes
-constexpr int kBlockKBytes = 128;     // K bytes per stage = one swizzle row
+constexpr int kBlockKBytes = 128;     // K bytes per TMA box = one swizzle row
 constexpr int kUmmaKBytes = 32;       // K bytes per tcgen05.mma
-constexpr int kNumThreads = 320;
-constexpr int kEpilogueWarp0 = 2;
+constexpr int kPrefetchTiles = 3;     // how many tiles ahead the activations are pulled into L2
+constexpr int kNumThreads = 384;       // three warpgroups: {TMA, MMA, 2 idle warps}, 2 x epilogue
+constexpr int kEpilogueWarp0 = 4;
+constexpr int kRegsLight = 64;         // registers per thread of warpgroup 0 after set-up
+constexpr int kRegsEpilogue = 216;     // and of the two epilogue warpgroups
 constexpr int kEpilogueWarps = 8;
 constexpr int kStageRows = 32;        // rows per epilogue warp
 constexpr int kStagingBytes = kStageRows * 128;
@@ -57,22 +67,57 @@ struct GemmDev {
     int seqlen;
     int qk_cols;
     int a_plane;  // plane of the 3-D A tensor map this launch reads
+    // ROTARY with whole sequences (M = n_seq * seqlen, seqlen >= 128): tiles are aligned to the
+    // sequences (seq_tiles per sequence, the last one shifted up to end at the sequence end) and a
+    // CTA takes a contiguous run of the list ordered by (tile-in-sequence, sequence), so the rows
+    // of successive tiles keep their positions and their sin/cos values stay in registers.
+    int seq_tiles;  // 0: plain tiling, tile t covers rows [128 t, 128 t + 128)
+    int n_seq;
+    int items_per_cta;
 };
 
+struct TrueTag { static constexpr bool value = true; };
+struct FalseTag { static constexpr bool value = false; };
+
+// The work list of a CTA: items w_begin, w_begin + w_step, ... < w_end; item -> first row.
+struct TileIter {
+    int w_begin, w_end, w_step;
+    __device__ __forceinline__ TileIter(const GemmDev &p, int m_first) {
+        if (p.seq_tiles > 0) {
+            w_begin = m_first * p.items_per_cta;
+            w_end = min(p.seq_tiles * p.n_seq, w_begin + p.items_per_cta);
+            w_step = 1;
+        } else {
+            w_begin = m_first;
+            w_end = p.num_m_tiles;
+            w_step = p.ctas_per_n;
+        }
+    }
+    // tile-in-sequence index (seq mode only)
+    __device__ __forceinline__ static int seq_index(const GemmDev &p, int w) { return w / p.n_seq; }
+    __device__ __forceinline__ static int seq_pos0(const GemmDev &p, int s) {
+        return min(s * kBlockM, p.seqlen - kBlockM);
+    }
+    __device__ __forceinline__ static int row0(const GemmDev &p, int w) {
+        if (p.seq_tiles > 0) {
+            const int s = w / p.n_seq;
+            return (w - s * p.n_seq) * p.seqlen + seq_pos0(p, s);
+        }
+        return w * kBlockM;
+    }
+};
 
 template <int EPI, int BN_MMA, int STAGES>
 struct SmemLayout {
-    static constexpr bool kRotary = (EPI == FLUKE_SM100_EPI_ROTARY);
     static constexpr int kMaxKBlocks = kWeightBytes / (BN_MMA * kBlockKBytes);  // 4 (BN 256) or 8 (BN 128)
-    static constexpr int kABytes = kBlockM * kBlockKBytes;
-    static constexpr int kBBytes = BN_MMA * kBlockKBytes;   // one K block of the weight tile
+    static constexpr int kABytes = kBlockM * kBlockKBytes;        // one K block of an A tile = one ring stage
+    static constexpr int kBBytes = BN_MMA * kBlockKBytes;         // one K block of the weight tile
     static constexpr int kOffW = 0;
     static constexpr int kOffA = kWeightBytes;
     static constexpr int kOffStaging = kOffA + STAGES * kABytes;
-    static constexpr int kOffTables = kOffStaging + kEpilogueWarps * kStagingBytes;
-    static constexpr int kOffScaleB = kOffTables + (kRotary ? 4 * 8192 : 0);  // per quadrant: sin 4 KB | cos 4 KB
-    static constexpr int kOffBars = kOffScaleB + (EPI == FLUKE_SM100_EPI_SILU ? 0 : BN_MMA * 4);
-    static constexpr int kNumBars = 2 * STAGES + 5 + 8;
+    static constexpr int kOffScaleB = kOffStaging + kEpilogueWarps * kStagingBytes;  // ROTARY: f32 [BN_MMA]
+    static constexpr int kOffBars = kOffScaleB + (EPI == FLUKE_SM100_EPI_ROTARY ? BN_MMA * 4 : 0);
+    static constexpr int kNumBars = 2 * STAGES + 5;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kTotal = kOffMisc + 16;
     static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
@@ -95,6 +140,10 @@ __device__ __forceinline__ float acc_to_float(uint32_t bits) {
     if constexpr (KIND == kKindI8) return static_cast<float>(static_cast<int>(bits));
     else return __uint_as_float(bits);
 }
+template <int KIND>
+__device__ __forceinline__ float2 acc_to_float2(uint32_t a, uint32_t b) {
+    return make_float2(acc_to_float<KIND>(a), acc_to_float<KIND>(b));
+}
 
 // Writes one 128-byte row (8 x 16-byte chunks held in v[0..31]) into a swizzled staging tile.
 __device__ __forceinline__ void stage_row(uint8_t *staging, uint32_t row, const uint32_t (&v)[32]) {
@@ -103,19 +152,6 @@ __device__ __forceinline__ void stage_row(uint8_t *staging, uint32_t row, const 
         uint4 q = make_uint4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
         *reinterpret_cast<uint4 *>(staging + sw128_offset(row, ch)) = q;
     }
-}
-
-// Bounded barrier between the two epilogue warps of a lane quadrant (one arrival per warp).
-__device__ __forceinline__ bool pair_barrier(uint64_t *bar, uint32_t parity, int lane,
-                                             volatile int *abort_flag) {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar);
-    return mbar_wait(bar, parity, abort_flag, 5);
-}
-
-__device__ __forceinline__ void ld4(const float *p, float (&v)[4]) {
-    const float4 t = *reinterpret_cast<const float4 *>(p);
-    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
 }
 
 template <int KIND, int EPI, int BN_MMA, int STAGES>
@@ -138,12 +174,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     uint64_t *empty_bar = bars + STAGES;
     uint64_t *tfull_bar = bars + 2 * STAGES;
     uint64_t *tempty_bar = bars + 2 * STAGES + 2;
-    uint64_t *w_bar = bars + 2 * STAGES + 4;          // resident weight tile loaded
-    uint64_t *tab_full_bar = bars + 2 * STAGES + 5;   // [4] tables of the quadrant are staged
-    uint64_t *tab_empty_bar = bars + 2 * STAGES + 9;  // [4] both warps are done reading them
+    uint64_t *w_bar = bars + 2 * STAGES + 4;      // resident weight tile loaded
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kOffMisc + 4);
-    float *sbs = reinterpret_cast<float *>(smem + L::kOffScaleB);  // weight scales of this N tile
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -161,10 +194,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             mbar_init(&tempty_bar[s], kEpilogueWarps);
         }
         mbar_init(w_bar, 1);
-        for (int s = 0; s < 4; ++s) {
-            mbar_init(&tab_full_bar[s], 2);
-            mbar_init(&tab_empty_bar[s], 2);
-        }
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tm_a);
@@ -173,29 +202,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         tma_prefetch_desc(&tm_out);
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
-    if (warp >= kEpilogueWarp0) {
-        // weight scales of the tile's columns (zeros past N), read by every epilogue thread
-        if constexpr (EPI != FLUKE_SM100_EPI_RAW && EPI != FLUKE_SM100_EPI_SILU) {
-            for (int j = threadIdx.x - 64; j < BN_MMA; j += kEpilogueWarps * 32) {
-                float v;
-                if (kDual) {
-                    const int col = n0 + (j % BN_OUT);
-                    v = col < p.N ? __ldg((j < BN_OUT ? p.scale_b : p.scale_b2) + col) : 0.f;
-                } else {
-                    v = n0 + j < p.N ? __ldg(p.scale_b + n0 + j) : 0.f;
-                }
-                sbs[j] = v;
-            }
-        }
+    if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
+        // weight scales of the tile's columns, read by every epilogue thread of the rotary kernel
+        float *sbs = reinterpret_cast<float *>(smem + L::kOffScaleB);
+        for (int j = threadIdx.x; j < BN_MMA; j += kNumThreads) sbs[j] = __ldg(p.scale_b + n0 + j);
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // The launch gives every thread 65536 / 384 registers; the loader and issuer need few, the
+    // epilogue threads hold a whole row segment plus rotary tables: each role branch below
+    // starts by resizing its warpgroup's share.
 
+    if (warp < kEpilogueWarp0) reg_dealloc<kRegsLight>();
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
+        // ------------------------------ TMA producer (one thread) ------------------
+        if (elect_one()) {
             mbar_arrive_expect_tx(w_bar, uint32_t(p.num_k_blocks) * L::kBBytes);
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                 uint8_t *sb = smem + L::kOffW + kb * L::kBBytes;
@@ -206,49 +229,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     tma_load_2d(sb, &tm_b, w_bar, kb * kBlockKBytes, n0);
                 }
             }
-        }
-        __syncwarp();
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int mt = m_first; mt < p.num_m_tiles && ok; mt += p.ctas_per_n) {
-            const int m0 = mt * kBlockM;
-            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, 1);
-                if (!ok) break;
-                if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const TileIter it(p, m_first);
+            // The CTAs that share an activation tile reach it at about the same time, so without
+            // help every tile load would pay the HBM latency. One of them (chosen by the tile
+            // index) asks for the tile kPrefetchTiles steps ahead to be brought into L2. With a
+            // single N tile nothing is shared and the ring alone covers the latency.
+            auto prefetch_tile = [&](int w) {
+                if (p.num_n_tiles > 1 && w < it.w_end && (w % p.num_n_tiles) == n_tile) {
+                    const int m0 = TileIter::row0(p, w);
+                    for (int kb = 0; kb < p.num_k_blocks; ++kb)
+                        tma_prefetch_l2_3d(&tm_a, kb * kBlockKBytes, m0, p.a_plane);
+                }
+            };
+            for (int d = 0; d < kPrefetchTiles; ++d) prefetch_tile(it.w_begin + d * it.w_step);
+            for (int w = it.w_begin; w < it.w_end && ok; w += it.w_step) {
+                const int m0 = TileIter::row0(p, w);
+                prefetch_tile(w + kPrefetchTiles * it.w_step);
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, 1);
+                    if (!ok) break;
                     mbar_arrive_expect_tx(&full_bar[stage], L::kABytes);
                     tma_load_3d(smem + L::kOffA + stage * L::kABytes, &tm_a, &full_bar[stage],
                                 kb * kBlockKBytes, m0, p.a_plane);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                __syncwarp();
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (!ok) {
+                // Give loads that are still in flight a bounded chance to land before the CTA's
+                // shared memory is released.
+                const long long t0 = clock64();
+                while (clock64() - t0 < (1ll << 22)) { }
             }
         }
-        if (!ok) {
-            // Give loads that are still in flight a bounded chance to land before the CTA's
-            // shared memory is released.
-            const long long t0 = clock64();
-            while (clock64() - t0 < (1ll << 22)) { }
-        }
+        __syncwarp();
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer --------------------------------
-        int stage = 0;
-        uint32_t phase = 0;
-        int local = 0;
-        bool ok = mbar_wait(w_bar, 0, abort_flag, 6);
-        for (int mt = m_first; mt < p.num_m_tiles && ok; mt += p.ctas_per_n, ++local) {
-            const int acc = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1;
-            ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, 2);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t d_tmem = tmem_base + acc * BN_MMA;
-            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                ok = mbar_wait(&full_bar[stage], phase, abort_flag, 3);
+        // ------------------------------ MMA issuer (one thread) --------------------
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = mbar_wait(w_bar, 0, abort_flag, 6);
+            const TileIter it(p, m_first);
+            for (int w = it.w_begin; w < it.w_end && ok; w += it.w_step, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, 2);
                 if (!ok) break;
                 tc_fence_after_sync();
-                if (lane == 0) {
+                const uint32_t d_tmem = tmem_base + acc * BN_MMA;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    ok = mbar_wait(&full_bar[stage], phase, abort_flag, 3);
+                    if (!ok) break;
+                    tc_fence_after_sync();
                     const uint64_t adesc =
                         make_smem_desc_sw128(smem_u32(smem + L::kOffA + stage * L::kABytes));
                     const uint64_t bdesc =
@@ -261,197 +296,282 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                     tc_commit(&empty_bar[stage]);
                     if (kb == p.num_k_blocks - 1) tc_commit(&tfull_bar[acc]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                __syncwarp();
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
-    } else {
+        __syncwarp();
+    } else if (warp >= kEpilogueWarp0) {
         // ------------------------------ epilogue ----------------------------------
+        // Accumulators leave tensor memory in the 16-lane x 256-bit shape: per load a thread
+        // (g = lane / 4, t = lane % 4) receives, for each group j of 8 columns, the columns
+        // 8j + 2t and 8j + 2t + 1 of rows g and g + 8 of the 16 addressed lanes. Two loads
+        // (lane offsets 0 and 16) cover the warp's quadrant, so a thread works on four rows
+        // (g + 8k) and on a quarter of the warp's columns. Those columns never change while the
+        // CTA lives (it owns one N tile), which lets every per-column factor of the epilogue --
+        // the weight scales, and with sequence-aligned tiling the rotary sin/cos values -- stay
+        // in registers: the epilogue reads no table from shared memory.
+        reg_alloc<kRegsEpilogue>();
         const int q = warp & 3;                           // TMEM lane quadrant this warp may read
-        const int ch = (warp - kEpilogueWarp0) >> 2;      // which half of the tile's columns
+        const int ch = (warp - kEpilogueWarp0) >> 2;      // which of the quadrant's two warps
+        const int g8 = lane >> 2, t4 = lane & 3;
         uint8_t *staging = smem + L::kOffStaging + (warp - kEpilogueWarp0) * kStagingBytes;
-        uint8_t *tables = smem + L::kOffTables + q * 8192;  // ROTARY only
-        const bool rotate = (EPI == FLUKE_SM100_EPI_ROTARY) && n0 < p.qk_cols;
+        const TileIter it(p, m_first);
         int local = 0;
-        uint32_t tab_phase = 0;
         bool ok = true;
-        for (int mt = m_first; mt < p.num_m_tiles && ok; mt += p.ctas_per_n, ++local) {
-            const int m0 = mt * kBlockM;
-            const int acc = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1;
-            const int row = m0 + q * 32 + lane;
-            const bool row_ok = row < p.M;
 
-            float sa = 0.f;
-            if constexpr (EPI != FLUKE_SM100_EPI_RAW) {
-                sa = p.scale_a ? (row_ok ? __ldg(p.scale_a + row) : 0.f) : p.const_scale_a;
-            }
-
-            // Rotary tables of the quadrant's 32 rows, staged once per tile: warp ch = 0 copies
-            // the sin rows, ch = 1 the cos rows (coalesced 16-byte loads, swizzled 128-byte rows).
-            if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
-                if (rotate) {
-                    const float *src = ch == 0 ? p.sin_tab : p.cos_tab;
+        // row scales of the thread's four rows of the tile that starts at row m0
+        auto load_sa = [&](int m0, float (&sa)[4]) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int id = j * 32 + lane;
-                        const int r = id >> 3, cc = id & 7;
-                        const int grow = m0 + q * 32 + r;
-                        const int pos = grow < p.M ? grow % p.seqlen : 0;
-                        const float4 v = __ldg(reinterpret_cast<const float4 *>(src + pos * 32) + cc);
-                        *reinterpret_cast<float4 *>(tables + ch * 4096 + sw128_offset(r, cc)) = v;
+            for (int k = 0; k < 4; ++k) {
+                const int row = m0 + q * 32 + g8 + 8 * k;
+                sa[k] = p.scale_a ? (row < p.M ? __ldg(p.scale_a + row) : 0.f) : p.const_scale_a;
+            }
+        };
+        // 4-byte store of two adjacent f16 outputs (columns 8j + 2t, +1 of the 64-column staging
+        // tile) of quadrant row r; conflict-free: the 8 rows of an instruction hit 8 chunks
+        auto stage_pair = [&](int r, int j, uint32_t v) {
+            *reinterpret_cast<uint32_t *>(staging + sw128_offset(r, j) + 4 * t4) = v;
+        };
+
+        if constexpr (EPI == FLUKE_SM100_EPI_RAW) {
+            // 32-bit accumulators, no scaling: thread = row, 32 columns per store
+            for (int w = it.w_begin; w < it.w_end && ok; w += it.w_step, ++local) {
+                const int m0 = TileIter::row0(p, w);
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 4);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA;
+                constexpr int kChunks = kWarpCols / 32;
+#pragma unroll 1
+                for (int chunk = 0; chunk < kChunks; ++chunk) {
+                    const int c0 = ch * kWarpCols + chunk * 32;
+                    const bool chunk_ok = n0 + c0 < p.N;
+                    uint32_t outw[32];
+                    if (chunk_ok) {
+                        tmem_ld_32x32(t_row + c0, outw);
+                        tmem_ld_wait();
                     }
-                    ok = pair_barrier(&tab_full_bar[q], tab_phase, lane, abort_flag);
-                    if (!ok) break;
+                    if (chunk == kChunks - 1) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+                    }
+                    if (!chunk_ok) continue;
+                    if (lane == 0) tma_store_wait_read<0>();
+                    __syncwarp();
+                    stage_row(staging, lane, outw);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_out, staging, n0 + c0, m0 + q * 32);
+                        tma_store_commit();
+                    }
                 }
             }
-
-            ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 4);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA;
-
-            constexpr int kChunkCols = (EPI == FLUKE_SM100_EPI_RAW) ? 32 : 64;
-            constexpr int kChunks = kWarpCols / kChunkCols;
-#pragma unroll 1
-            for (int chunk = 0; chunk < kChunks; ++chunk) {
-                const int c0 = ch * kWarpCols + chunk * kChunkCols;  // column inside the tile
-                const bool chunk_ok = n0 + c0 < p.N;  // N % 64 == 0: a chunk is all in or all out
-                uint32_t outw[32];  // one 128-byte output row segment
-
-                if (!chunk_ok) {
-                    // columns past N: nothing to compute or store
-                } else if constexpr (EPI == FLUKE_SM100_EPI_RAW) {
-                    tmem_ld_32x32(t_row + c0, outw);
-                    tmem_ld_wait();
-                } else if constexpr (EPI == FLUKE_SM100_EPI_SILU) {
+        } else if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
+            // Thread = output row (32-lane x 32-bit loads). A tile is four heads; warp `ch` owns
+            // heads 2*ch and 2*ch+1. The 32 sin and 32 cos values of the row's position stay in
+            // registers: with sequence-aligned tiling they are loaded once per run of tiles with
+            // the same tile-in-sequence index, otherwise at the start of every tile.
+            static_assert(BN_OUT == 256, "two heads per epilogue warp");
+            const float *sbs = reinterpret_cast<const float *>(smem + L::kOffScaleB);
+            const bool rotate = n0 < p.qk_cols;
+            float2 sn2[16], cs2[16];  // pairs (e, e+1) as they come out of the 16-byte loads
+            auto load_tables = [&](int pos) {
+                const float4 *s4 = reinterpret_cast<const float4 *>(p.sin_tab + pos * 32);
+                const float4 *c4 = reinterpret_cast<const float4 *>(p.cos_tab + pos * 32);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint32_t g[32], u[32];
-                        tmem_ld_32x32(t_row + c0 + half * 32, g);
-                        tmem_ld_32x32(t_row + BN_OUT + c0 + half * 32, u);
-                        float sg[32], su[32];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            // weight scales through L1 (the same address in every lane); N % 128 == 0 here
-                            const float4 a4 = __ldg(reinterpret_cast<const float4 *>(p.scale_b + n0 + c0 + half * 32) + i);
-                            const float4 b4 = __ldg(reinterpret_cast<const float4 *>(p.scale_b2 + n0 + c0 + half * 32) + i);
-                            sg[4 * i] = a4.x; sg[4 * i + 1] = a4.y; sg[4 * i + 2] = a4.z; sg[4 * i + 3] = a4.w;
-                            su[4 * i] = b4.x; su[4 * i + 1] = b4.y; su[4 * i + 2] = b4.z; su[4 * i + 3] = b4.w;
+                for (int j = 0; j < 8; ++j) {
+                    const float4 sv = __ldg(s4 + j), cv = __ldg(c4 + j);
+                    sn2[2 * j] = make_float2(sv.x, sv.y);
+                    sn2[2 * j + 1] = make_float2(sv.z, sv.w);
+                    cs2[2 * j] = make_float2(cv.x, cv.y);
+                    cs2[2 * j + 1] = make_float2(cv.z, cv.w);
+                }
+            };
+            const bool seq_mode = p.seq_tiles > 0;
+            int cur_s = -1;
+            auto load_sa1 = [&](int m0) {
+                const int row = m0 + q * 32 + lane;
+                return p.scale_a ? (row < p.M ? __ldg(p.scale_a + row) : 0.f) : p.const_scale_a;
+            };
+            float sa_next = it.w_begin < it.w_end ? load_sa1(TileIter::row0(p, it.w_begin)) : 0.f;
+            for (int w = it.w_begin; w < it.w_end && ok; w += it.w_step, ++local) {
+                const int m0 = TileIter::row0(p, w);
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                const float sa = sa_next;
+                const float2 sa2 = make_float2(sa, sa);
+                if (w + it.w_step < it.w_end) sa_next = load_sa1(TileIter::row0(p, w + it.w_step));
+                if (rotate) {
+                    if (seq_mode) {
+                        // the positions only change when the tile-in-sequence index does
+                        const int s_idx = TileIter::seq_index(p, w);
+                        if (s_idx != cur_s) {
+                            cur_s = s_idx;
+                            load_tables(TileIter::seq_pos0(p, s_idx) + q * 32 + lane);
                         }
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float o[2];
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) {
-                                const int e = 2 * i + j;
-                                const float gate = (acc_to_float<KIND>(g[e]) * sa) * sg[e];
-                                const float up = (acc_to_float<KIND>(u[e]) * sa) * su[e];
-                                const float sig = 0.5f * tanh_approx(0.5f * gate) + 0.5f;
-                                o[j] = gate * sig * up;
-                            }
-                            outw[half * 16 + i] = pack_half2(o[0], o[1]);
-                        }
+                    } else {
+                        const int grow = m0 + q * 32 + lane;
+                        load_tables(grow < p.M ? grow % p.seqlen : 0);
                     }
-                } else if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
-                    // One head: pairs (i, i+32). Two passes of 16 pairs; every load of a pass is
-                    // issued before its first use.
+                }
+
+                ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 4);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA;
+
+                // One head's 128-byte output row segment; kRot is a type so that the rotation is
+                // compiled in or out of the inner loop instead of branched around per pair.
+                auto head_math = [&](auto rot_tag, int c0, uint32_t (&outw)[32]) {
+                    constexpr bool kRot = decltype(rot_tag)::value;
 #pragma unroll
                     for (int sub = 0; sub < 2; ++sub) {
+                        // rotation pairs 16*sub .. 16*sub+15: columns (i, i+32) of the head
                         uint32_t lo[16], hi[16];
                         tmem_ld_32x16(t_row + c0 + sub * 16, lo);
                         tmem_ld_32x16(t_row + c0 + 32 + sub * 16, hi);
-                        float bl[16], bh[16], sn[16], cs[16];
+                        float4 bl4[4], bh4[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            float t4[4];
-                            ld4(sbs + c0 + sub * 16 + 4 * i, t4);
-                            bl[4 * i] = t4[0]; bl[4 * i + 1] = t4[1]; bl[4 * i + 2] = t4[2]; bl[4 * i + 3] = t4[3];
-                            ld4(sbs + c0 + 32 + sub * 16 + 4 * i, t4);
-                            bh[4 * i] = t4[0]; bh[4 * i + 1] = t4[1]; bh[4 * i + 2] = t4[2]; bh[4 * i + 3] = t4[3];
-                            if (rotate) {
-                                ld4(reinterpret_cast<const float *>(tables + sw128_offset(lane, sub * 4 + i)), t4);
-                                sn[4 * i] = t4[0]; sn[4 * i + 1] = t4[1]; sn[4 * i + 2] = t4[2]; sn[4 * i + 3] = t4[3];
-                                ld4(reinterpret_cast<const float *>(tables + 4096 + sw128_offset(lane, sub * 4 + i)), t4);
-                                cs[4 * i] = t4[0]; cs[4 * i + 1] = t4[1]; cs[4 * i + 2] = t4[2]; cs[4 * i + 3] = t4[3];
-                            }
+                            bl4[i] = *reinterpret_cast<const float4 *>(sbs + c0 + sub * 16 + 4 * i);
+                            bh4[i] = *reinterpret_cast<const float4 *>(sbs + c0 + 32 + sub * 16 + 4 * i);
                         }
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            float o_lo[2], o_hi[2];
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) {
-                                const int e = 2 * i + j;
-                                const float x0 = (acc_to_float<KIND>(lo[e]) * sa) * bl[e];
-                                const float x1 = (acc_to_float<KIND>(hi[e]) * sa) * bh[e];
-                                if (rotate) {
-                                    // fixed operation order (no compiler-chosen contraction)
-                                    o_lo[j] = __fmaf_rn(x0, cs[e], -__fmul_rn(x1, sn[e]));
-                                    o_hi[j] = __fmaf_rn(x0, sn[e], __fmul_rn(x1, cs[e]));
-                                } else {
-                                    o_lo[j] = x0;
-                                    o_hi[j] = x1;
-                                }
+                            const int e = 2 * i;
+                            // (acc*sa)*sb, then the rotation in a fixed operation order (no
+                            // compiler-chosen contraction): lo' = fma(x0, cos, -(x1*sin)),
+                            // hi' = fma(x0, sin, x1*cos)
+                            const float2 bl2 = (i & 1) ? make_float2(bl4[i >> 1].z, bl4[i >> 1].w)
+                                                       : make_float2(bl4[i >> 1].x, bl4[i >> 1].y);
+                            const float2 bh2 = (i & 1) ? make_float2(bh4[i >> 1].z, bh4[i >> 1].w)
+                                                       : make_float2(bh4[i >> 1].x, bh4[i >> 1].y);
+                            const float2 x0 = mul2(mul2(acc_to_float2<KIND>(lo[e], lo[e + 1]), sa2), bl2);
+                            const float2 x1 = mul2(mul2(acc_to_float2<KIND>(hi[e], hi[e + 1]), sa2), bh2);
+                            float2 o_lo = x0, o_hi = x1;
+                            if constexpr (kRot) {
+                                const float2 m = mul2(x1, sn2[sub * 8 + i]);
+                                o_lo = fma2(x0, cs2[sub * 8 + i], make_float2(-m.x, -m.y));
+                                o_hi = fma2(x0, sn2[sub * 8 + i], mul2(x1, cs2[sub * 8 + i]));
                             }
-                            outw[sub * 8 + i] = pack_half2(o_lo[0], o_lo[1]);
-                            outw[16 + sub * 8 + i] = pack_half2(o_hi[0], o_hi[1]);
+                            outw[sub * 8 + i] = pack_half2(o_lo.x, o_lo.y);
+                            outw[16 + sub * 8 + i] = pack_half2(o_hi.x, o_hi.y);
                         }
                     }
-                } else {
-                    // DEQUANT / DEQUANT2: 64 columns in two passes of 32
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint32_t a[32];
-                        tmem_ld_32x32(t_row + c0 + half * 32, a);
-                        float bv[32];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float t4[4];
-                            ld4(sbs + c0 + half * 32 + 4 * i, t4);
-                            bv[4 * i] = t4[0]; bv[4 * i + 1] = t4[1]; bv[4 * i + 2] = t4[2]; bv[4 * i + 3] = t4[3];
-                        }
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float o[2];
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) {
-                                const float v = acc_to_float<KIND>(a[2 * i + j]);
-                                if constexpr (EPI == FLUKE_SM100_EPI_DEQUANT) o[j] = v * (sa * bv[2 * i + j]);
-                                else o[j] = (v * sa) * bv[2 * i + j];
-                            }
-                            outw[half * 16 + i] = pack_half2(o[0], o[1]);
-                        }
+                };
+#pragma unroll 1
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    const int c0 = (2 * ch + h2) * 64;  // first column of the head inside the tile
+                    uint32_t outw[32];
+                    if (rotate) head_math(TrueTag{}, c0, outw);
+                    else head_math(FalseTag{}, c0, outw);
+                    if (h2 == 1) {
+                        // Every TMEM read of this accumulator is done: hand it back to the MMA
+                        // warp before the slower store path.
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
                     }
-                }
-
-                if (chunk == kChunks - 1) {
-                    // Every TMEM read of this accumulator is done: hand it back to the MMA warp
-                    // before the slower store path.
-                    tc_fence_before_sync();
+                    if (lane == 0) tma_store_wait_read<0>();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+                    stage_row(staging, lane, outw);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_out, staging, n0 + c0, m0 + q * 32);
+                        tma_store_commit();
+                    }
                 }
+            }
+        } else {
+            // SILU: warp `ch` owns output columns [64 ch, 64 ch + 64) of the tile's 128: gate
+            // accumulators at those columns, up accumulators 128 columns further.
+            // DEQUANT / DEQUANT2: columns [64 ch, 64 ch + 64) of the tile's 128.
+            static_assert(BN_OUT == 128, "64 output columns per epilogue warp");
+            const int c0 = ch * 64;
+            const bool cols_ok = n0 + c0 < p.N;  // N % 64 == 0: the warp's columns are all in or all out
+            float2 sc[8], sc_up[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int col = n0 + c0 + 8 * j + 2 * t4;
+                sc[j] = cols_ok ? __ldg(reinterpret_cast<const float2 *>(p.scale_b + col)) : make_float2(0.f, 0.f);
+                if constexpr (kDual) {
+                    // the epilogue works on gate/2: halving the scale is exact
+                    sc[j] = make_float2(0.5f * sc[j].x, 0.5f * sc[j].y);
+                    sc_up[j] = cols_ok ? __ldg(reinterpret_cast<const float2 *>(p.scale_b2 + col)) : make_float2(0.f, 0.f);
+                }
+            }
+            float sa_next[4];
+            if (it.w_begin < it.w_end) load_sa(TileIter::row0(p, it.w_begin), sa_next);
+            for (int w = it.w_begin; w < it.w_end && ok; w += it.w_step, ++local) {
+                const int m0 = TileIter::row0(p, w);
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                float2 sa2[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) sa2[k] = make_float2(sa_next[k], sa_next[k]);
+                if (w + it.w_step < it.w_end) load_sa(TileIter::row0(p, w + it.w_step), sa_next);
 
-                if (!chunk_ok) continue;
-                if (lane == 0) tma_store_wait_read<0>();
-                __syncwarp();
-                stage_row(staging, lane, outw);
+                ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 4);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t t_base = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA + c0;
+#pragma unroll
+                for (int hr = 0; hr < 2; ++hr) {  // rows g, g+8 then g+16, g+24
+                    uint32_t a[32], u[32];
+                    if (cols_ok) {
+                        tmem_ld_16x256_x8(t_base + (uint32_t(16 * hr) << 16), a);
+                        if constexpr (kDual) tmem_ld_16x256_x8(t_base + (uint32_t(16 * hr) << 16) + BN_OUT, u);
+                        tmem_ld_wait();
+                    }
+                    if (hr == 1) {
+                        // Every TMEM read of this accumulator is done: hand it back to the MMA
+                        // warp before the arithmetic and the store.
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+                    }
+                    if (!cols_ok) continue;
+                    if (hr == 0) {
+                        // the store of the previous tile must have read the staging tile
+                        if (lane == 0) tma_store_wait_read<0>();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int k2 = 0; k2 < 2; ++k2) {
+                        const int k = 2 * hr + k2;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float2 v = acc_to_float2<KIND>(a[4 * j + 2 * k2], a[4 * j + 2 * k2 + 1]);
+                            float2 o;
+                            if constexpr (EPI == FLUKE_SM100_EPI_SILU) {
+                                // h = gate/2 = (acc_g*sa)*(sg/2); silu(gate) = gate *
+                                // (0.5*tanh(h)+0.5) = h*tanh(h) + h
+                                const float2 h = mul2(mul2(v, sa2[k]), sc[j]);
+                                const float2 up = mul2(mul2(acc_to_float2<KIND>(u[4 * j + 2 * k2], u[4 * j + 2 * k2 + 1]), sa2[k]), sc_up[j]);
+                                const float2 t = make_float2(tanh_approx(h.x), tanh_approx(h.y));
+                                o = mul2(fma2(h, t, h), up);
+                            } else if constexpr (EPI == FLUKE_SM100_EPI_DEQUANT) {
+                                o = mul2(v, mul2(sa2[k], sc[j]));
+                            } else {
+                                o = mul2(mul2(v, sa2[k]), sc[j]);
+                            }
+                            stage_pair(g8 + 8 * k, j, pack_half2(o.x, o.y));
+                        }
+                    }
+                }
+                if (!cols_ok) continue;
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     tma_store_2d(&tm_out, staging, n0 + c0, m0 + q * 32);
                     tma_store_commit();
-                }
-            }
-            if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
-                if (rotate) {
-                    // both warps of the quadrant are done with the tables of this tile
-                    ok = pair_barrier(&tab_empty_bar[q], tab_phase, lane, abort_flag);
-                    tab_phase ^= 1u;
                 }
             }
         }
@@ -462,6 +582,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -553,9 +674,20 @@ int plan_build(const fluke_sm100_gemm_t *g, int a_planes, GemmPlan *plan) {
     const int sms = device_sm_count();
     if (p.num_n_tiles > sms || p.num_k_blocks > SmemLayout<EPI, BN_MMA, STAGES>::kMaxKBlocks)
         return (int)cudaErrorInvalidValue;  // N tile count / K beyond what one resident tile covers
+    p.seq_tiles = 0; p.n_seq = 0; p.items_per_cta = 0;
+    int items = p.num_m_tiles;
+    if (EPI == FLUKE_SM100_EPI_ROTARY && p.seqlen >= kBlockM && g->M % p.seqlen == 0) {
+        p.seq_tiles = (p.seqlen + kBlockM - 1) / kBlockM;
+        p.n_seq = g->M / p.seqlen;
+        items = p.seq_tiles * p.n_seq;
+    }
     int per_n = sms / p.num_n_tiles;
-    if (per_n > p.num_m_tiles) per_n = p.num_m_tiles;
+    if (per_n > items) per_n = items;
     if (per_n < 1) per_n = 1;
+    if (p.seq_tiles > 0) {
+        p.items_per_cta = (items + per_n - 1) / per_n;
+        per_n = (items + p.items_per_cta - 1) / p.items_per_cta;  // no CTA without work
+    }
     p.ctas_per_n = per_n;
     plan->grid = p.num_m_tiles > 0 ? per_n * p.num_n_tiles : 0;
     return 0;
@@ -585,11 +717,11 @@ int launch(const fluke_sm100_gemm_t *g, cudaStream_t stream) {
 }
 
 // Tile shapes: 128 x 128 (K up to 1024 resident) for the plain GEMMs; 128 x 256 (one UMMA of
-// N = 256 per K step, K up to 512 resident) for the two fused transformer kernels. The last
-// number is the depth of the ring of 16 KB activation stages that fits beside the resident
-// weight tile, the store staging and (rotary) the tables.
-constexpr int kPlainBN = 128, kPlainStages = 4;
-constexpr int kFusedBN = 256, kFusedStages = 2, kSiluStages = 4;
+// N = 256 per K step, K up to 512 resident) for the two fused transformer kernels. Beside the
+// resident weight tile and 32 KB of store staging there is room for a ring of four 16 KB
+// activation stages.
+constexpr int kPlainBN = 128, kFusedBN = 256;
+constexpr int kPlainStages = 4, kFusedStages = 4, kSiluStages = 4;
 
 template <int KIND>
 int dispatch(const fluke_sm100_gemm_t *g, cudaStream_t s) {
@@ -629,6 +761,7 @@ extern "C" int fluke_sm100_gemm(const fluke_sm100_gemm_t *g, void *stream) {
     if (g->kind == FLUKE_SM100_KIND_F8) return dispatch<kKindF8>(g, s);
     return (int)cudaErrorInvalidValue;
 }
+
 
 extern "C" int fluke_sm100_compute_capability(int device_index) {
     int major = 0, minor = 0;

@@ -42,6 +42,16 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Per-warpgroup register budget (all four warps of the warpgroup execute it together).
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // Orders generic-proxy shared-memory writes before later async-proxy (TMA, tcgen05) reads.
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -127,6 +137,12 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
           "r"(c0), "r"(c1), "r"(c2)
         : "memory");
+}
+// Brings a box into L2 only (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap *m, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int c0,
                                              int c1) {
@@ -261,8 +277,49 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         : "r"(taddr)
         : "memory");
 }
+// 16 lanes x 256 bits, repeated over 8 groups of 8 columns: thread (g = lane/4, t = lane%4) of
+// the warp receives in r[4j .. 4j+3] the 32-bit cells (row g, columns 8j+2t, 8j+2t+1) and
+// (row g+8, the same two columns) of the 16 lanes starting at the address's lane.
+__device__ __forceinline__ void tmem_ld_16x256_x8(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Packed pairs of f32: one instruction per two IEEE round-to-nearest results (each half is
+// bit-identical to the scalar mul.rn / fma.rn).
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 c;
+    asm("add.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<uint64_t &>(c))
+        : "l"(reinterpret_cast<const uint64_t &>(a)), "l"(reinterpret_cast<const uint64_t &>(b)));
+    return c;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 c;
+    asm("mul.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<uint64_t &>(c))
+        : "l"(reinterpret_cast<const uint64_t &>(a)), "l"(reinterpret_cast<const uint64_t &>(b)));
+    return c;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<uint64_t &>(d))
+        : "l"(reinterpret_cast<const uint64_t &>(a)), "l"(reinterpret_cast<const uint64_t &>(b)),
+          "l"(reinterpret_cast<const uint64_t &>(c)));
+    return d;
 }
 
 // Byte offset of 16-byte chunk `chunk16` of row `row` inside a tile of 128-byte rows stored in

@@ -29,9 +29,10 @@ inline encode_tiled_fn get_encode_tiled() {
 // Row-major 2-D tensor [rows, cols] with `row_stride_bytes` between rows (multiple of 16),
 // copied in boxes of box_rows x box_cols elements; box_cols * elem_bytes must be 128 when the
 // 128-byte swizzle is used. Out-of-range parts of a box read as zero and are not written.
-inline int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, uint32_t elem_bytes,
-                        const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
-                        uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+// make_tmap_2d_sw takes the swizzle mode itself (the box row must span exactly that many bytes).
+inline int make_tmap_2d_sw(CUtensorMap *m, CUtensorMapDataType dt, const void *base, uint64_t rows,
+                           uint64_t cols, uint64_t row_stride_bytes, uint32_t box_rows,
+                           uint32_t box_cols, CUtensorMapSwizzle swizzle) {
     encode_tiled_fn fn = get_encode_tiled();
     if (!fn) return (int)cudaErrorNotSupported;
     if ((reinterpret_cast<uintptr_t>(base) & 15u) || (row_stride_bytes & 15u))
@@ -40,12 +41,18 @@ inline int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, uint32_t elem_by
     cuuint64_t strides[1] = {row_stride_bytes};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
-    (void)elem_bytes;
     CUresult r = fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+inline int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, uint32_t elem_bytes,
+                        const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                        uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+    (void)elem_bytes;
+    return make_tmap_2d_sw(m, dt, base, rows, cols, row_stride_bytes, box_rows, box_cols,
+                           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 // Row-major 3-D tensor [planes, rows, cols]; boxes are 1 x box_rows x box_cols.

@@ -79,6 +79,36 @@ def test_base_gemm_f16_bit_exact_vs_oracle(m, n, k):
     assert (torch.from_numpy(got.astype(np.float32)) - ref).abs().max() < 0.05
 
 
+def test_accumulators_beyond_2_pow_22_stay_bit_exact(be):
+    """The epilogues convert int32 -> f32 with an integer-add trick that is exact below 2^22 and
+    must fall back to the plain conversion above it: rows and weight rows of +-127/-128 drive
+    |acc| up to 512 * 128 * 128 = 2^23 in some output positions and leave others ordinary."""
+    g = torch.Generator().manual_seed(22)
+    m = 300
+    a = i8(g, m, 512)
+    a[5] = 127; a[70] = -128; a[131] = -127; a[299] = 127
+    sa = torch.rand(m, generator=g) * 0.02 + 0.001
+    w = i8(g, 1536, 512)
+    w[3] = 127; w[40] = -128; w[1000] = 127; w[1535] = -127; w[1030] = -128
+    sb = torch.rand(1536, generator=g) * 0.001 + 0.0001
+    A, W, SA, SB = a.to(DEV), w.to(DEV), sa.to(DEV), sb.to(DEV)
+    assert int(ops.gemm_i8_s32(A, W).abs().max()) >= 1 << 22
+    got = ops.gemm_i8(A, W, SA, SB).cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), port.gemm_i8(a.numpy(), w.numpy(), sa.numpy(), sb.numpy()).view(np.uint16))
+    sin, cos = prep.rotary_tables(150, 64)
+    got = ops.qkv_rotary_i8(be, A, W, SA, SB, sin.to(DEV), cos.to(DEV), 150).cpu().numpy()
+    exp = port.qkv_rotary_i8(a.numpy(), w.numpy(), sa.numpy(), sb.numpy(), sin.numpy(), cos.numpy(), 150)
+    assert np.array_equal(got.view(np.uint16), exp.view(np.uint16))
+    wg, wu = i8(g, 2048, 512), i8(g, 2048, 512)
+    wg[7] = 127; wu[7] = -128; wg[2047] = -127; wu[100] = 127
+    sg, su = torch.rand(2048, generator=g) * 1e-4 + 1e-5, torch.rand(2048, generator=g) * 1e-4 + 1e-5
+    got = ops.gated_mlp_i8(be, A, wg.to(DEV), wu.to(DEV), SA, sg.to(DEV), su.to(DEV)).cpu().numpy().astype(np.float32)
+    exp = port.gated_mlp_i8(a.numpy(), wg.numpy(), wu.numpy(), sa.numpy(), sg.numpy(), su.numpy()).astype(np.float32)
+    assert np.isfinite(got).all() == np.isfinite(exp).all()
+    fin = np.isfinite(exp) & np.isfinite(got)
+    assert np.abs(got - exp)[fin].max() <= TOL_REL_RMS * np.sqrt((exp[fin] ** 2).mean())
+
+
 def test_down_proj_writes_into_a_wider_buffer():
     g = torch.Generator().manual_seed(3)
     a, b = i8(g, 200, 768), i8(g, 128, 768)
@@ -96,7 +126,7 @@ def _qkv_inputs(m, g):
     return a, sa, w, sb
 
 
-@pytest.mark.parametrize("batch,seqlen", [(4, 16), (1, 256), (3, 100), (5, 1000), (1, 1), (2, 77)])
+@pytest.mark.parametrize("batch,seqlen", [(4, 16), (1, 256), (3, 100), (5, 1000), (1, 1), (2, 77), (3, 130), (2, 128), (40, 300)])
 def test_qkv_rotary_bit_exact_vs_oracle(be, batch, seqlen):
     m = batch * seqlen
     a, sa, w, sb = _qkv_inputs(m, torch.Generator().manual_seed(m))
