@@ -348,10 +348,12 @@ def run_ours(args):
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) / reps * 1e3   # microseconds
         us_layer, us_xdown = time_mask(7), time_mask(1)
-        per_kernel = {"layer_total": us_layer, "x_down_gemm": us_xdown, "lstm_persist_kernel": us_layer - us_xdown}
+        form = flib.load().fluke_sm100_lstm_last_form()
+        kname = {1: "lstm_cluster_kernel", 2: "lstm_persist_kernel"}.get(form, "lstm_step_kernel")
+        per_kernel = {"layer_total": us_layer, "x_down_gemm": us_xdown, kname: us_layer - us_xdown}
         flops = T * (2.0 * B * (2 * R) * (4 * H) + 2.0 * B * R * H)   # f16 gate contraction + int8 hh projection
-        achieved = flops / (per_kernel["lstm_persist_kernel"] * 1e-6) / 1e12
-        roofline = {"kernel": "lstm_persist_kernel", "bound": "tensor", "achieved": round(achieved, 2),
+        achieved = flops / (per_kernel[kname] * 1e-6) / 1e12
+        roofline = {"kernel": kname, "bound": "tensor", "achieved": round(achieved, 2),
                     "peak": peaks["tf_sustained"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tf_sustained"], 4),
                     "peak_source": f"{peaks['source']} bf16 GEMM, sustained", "traffic": None,
                     "flops_per_launch": flops, "us_per_launch": {k: round(v, 3) for k, v in per_kernel.items()}}

@@ -124,9 +124,15 @@ int fluke_sm100_lstm_layer(const void *layer /* const fluke_flstm_layer_t* */, v
 /* Launch only some kernel classes of the layer: 1 = x_down GEMM, 2 = per-step down-projection,
  * 4 = per-step fused step (7 = the layer). For timing one class alone. */
 int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, void *stream);
-/* 1 (default): run the recurrence of a layer as persistent cooperative launches when the shape
- * is covered (R = 128, H a multiple of 128 up to 1024); 0: always two launches per timestep. */
-void fluke_sm100_set_lstm_persistent(int enabled);
+/* 1 (default): run the recurrence of a layer as one launch, with the exchange inside thread-block
+ * clusters where shape and device allow (R = 128, H a multiple of 64 up to 768), else through L2
+ * (R = 128, H a multiple of 128 up to 1024); 2: the L2-exchange form only; 0: always two launches
+ * per timestep. */
+void fluke_sm100_set_lstm_persistent(int mode);
+/* Which form the last whole-layer call used: 1 cluster exchange, 2 L2 exchange, 0 per step. */
+int fluke_sm100_lstm_last_form(void);
+/* Row tiles (clusters) of the cluster form that run at once for hidden size H; 0 = unavailable. */
+int fluke_sm100_lstm_cluster_capacity(int H);
 
 #ifdef __cplusplus
 }

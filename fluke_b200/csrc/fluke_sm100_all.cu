@@ -5,5 +5,6 @@
 #include "gemm_sm100.cu"
 #include "lstm_sm100.cu"
 #include "lstm_persist_sm100.cu"
+#include "lstm_cluster_sm100.cu"
 #include "lstm_noalloc_sm100.cu"
 #include "mma_peak_sm100.cu"

@@ -27,8 +27,8 @@
 // that all CTAs observe.
 //
 // Arithmetic is that of lstm_step_kernel and of the dequant GEMM epilogue, except that the two
-// K halves are accumulated x_down first and tanh is evaluated as 1 - 2/(exp(2c)+1) with the
-// fast exponential (absolute error ~1e-7, far below one int8 code).
+// K halves are accumulated x_down first and tanh is evaluated with the fast exponential (see
+// lstm_cell_pair).
 #include <fluke/fluke.h>
 
 #include "fluke_sm100.h"
@@ -147,16 +147,45 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "memory");
 }
 
-__device__ __forceinline__ float p_hard_sigmoid(float x) {
-    return fmaxf(0.f, fminf(1.f, __fmaf_rn(x, 0.2f, 0.5f)));
+// The cell update of two adjacent hidden units of one row, in packed f32x2 arithmetic where the
+// instruction set has it. gi..go: the accumulator bits (f32) of the four gates of units u, u+1;
+// bi..bo: their biases; c: the two cell values, updated in place. Returns the two int8 codes of
+// h in bits 0-7 and 8-15.
+//   gates   i, f, o = clamp(0.2 (acc + b) + 0.5, 0, 1) as one saturating fma each,
+//           g = clamp(acc + b, -1, 1)
+//   cell    c = fma(f, c, i * g)
+//   hidden  h = o * tanh(c), tanh as 1 - 2 / (exp(2c) + 1) with the fast exponential (absolute
+//           error ~1e-7, far below one int8 code); code = trunc(127 h +- 0.5)
+__device__ __forceinline__ float p_sat_fma(float x, float a, float b) {
+    float y;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(x), "f"(a), "f"(b));
+    return y;
 }
-__device__ __forceinline__ float p_tanh(float x) {
-    return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
-}
-__device__ __forceinline__ int p_quant_h(float h) {
-    const float hs = __fmul_rn(h, 127.0f);
-    const float half = fmaxf(-0.5f, fminf(0.5f, hs * 1e30f));
-    return __float2int_rz(hs + half);
+__device__ __forceinline__ uint32_t lstm_cell_pair(uint32_t gi0, uint32_t gi1, uint32_t gf0, uint32_t gf1,
+                                                   uint32_t gg0, uint32_t gg1, uint32_t go0, uint32_t go1,
+                                                   float2 bi, float2 bf, float2 bg, float2 bo, float2 &c) {
+    const float2 pi = add2(make_float2(__uint_as_float(gi0), __uint_as_float(gi1)), bi);
+    const float2 pf = add2(make_float2(__uint_as_float(gf0), __uint_as_float(gf1)), bf);
+    const float2 pg = add2(make_float2(__uint_as_float(gg0), __uint_as_float(gg1)), bg);
+    const float2 po = add2(make_float2(__uint_as_float(go0), __uint_as_float(go1)), bo);
+    const float2 i_a = make_float2(p_sat_fma(pi.x, 0.2f, 0.5f), p_sat_fma(pi.y, 0.2f, 0.5f));
+    const float2 f_a = make_float2(p_sat_fma(pf.x, 0.2f, 0.5f), p_sat_fma(pf.y, 0.2f, 0.5f));
+    const float2 o_a = make_float2(p_sat_fma(po.x, 0.2f, 0.5f), p_sat_fma(po.y, 0.2f, 0.5f));
+    const float2 g_a = make_float2(fmaxf(-1.f, fminf(1.f, pg.x)), fmaxf(-1.f, fminf(1.f, pg.y)));
+    c = fma2(f_a, c, mul2(i_a, g_a));
+    // exp(2c) = 2^(c * 2 log2 e)
+    const float2 t = mul2(c, make_float2(2.885390043f, 2.885390043f));
+    float ex, ey;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(t.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ey) : "f"(t.y));
+    const float2 den = add2(make_float2(ex, ey), make_float2(1.f, 1.f));
+    const float2 q = make_float2(__fdividef(2.0f, den.x), __fdividef(2.0f, den.y));
+    const float2 th = add2(make_float2(1.f, 1.f), make_float2(-q.x, -q.y));
+    const float2 hs = mul2(mul2(o_a, th), make_float2(127.f, 127.f));
+    // round half away from zero: add 0.5 with the sign of the value, then truncate
+    const float hx = hs.x + __uint_as_float(0x3F000000u | (__float_as_uint(hs.x) & 0x80000000u));
+    const float hy = hs.y + __uint_as_float(0x3F000000u | (__float_as_uint(hs.y) & 0x80000000u));
+    return (uint32_t(__float2int_rz(hx)) & 0xFFu) | ((uint32_t(__float2int_rz(hy)) & 0xFFu) << 8);
 }
 
 template <int UNITS>
@@ -309,16 +338,17 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             if (g < n_local) {
                 const int row = tile * 128 + q * 32 + lane;
                 const bool row_ok = row < p.B;
-                float c[UNITS];
+                float2 c2[UNITS / 2];  // the cell state of the slice, as pairs of adjacent units
                 if (row_ok) {
 #pragma unroll
                     for (int v = 0; v < UNITS / 4; ++v) {
                         const float4 c4 = *reinterpret_cast<const float4 *>(p.c + int64_t(row) * p.H + n0 + 4 * v);
-                        c[4 * v] = c4.x; c[4 * v + 1] = c4.y; c[4 * v + 2] = c4.z; c[4 * v + 3] = c4.w;
+                        c2[2 * v] = make_float2(c4.x, c4.y);
+                        c2[2 * v + 1] = make_float2(c4.z, c4.w);
                     }
                 } else {
 #pragma unroll
-                    for (int v = 0; v < UNITS; ++v) c[v] = 0.f;
+                    for (int v = 0; v < UNITS / 2; ++v) c2[v] = make_float2(0.f, 0.f);
                 }
                 const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + g * kPAccStride;
                 unsigned int *h_ready = p.flags + tile;
@@ -351,20 +381,14 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                             const float4 bf = *reinterpret_cast<const float4 *>(sbias + 1 * UNITS + u);
                             const float4 bg = *reinterpret_cast<const float4 *>(sbias + 2 * UNITS + u);
                             const float4 bo = *reinterpret_cast<const float4 *>(sbias + 3 * UNITS + u);
-                            const float bis[4] = {bi.x, bi.y, bi.z, bi.w}, bfs[4] = {bf.x, bf.y, bf.z, bf.w};
-                            const float bgs[4] = {bg.x, bg.y, bg.z, bg.w}, bos[4] = {bo.x, bo.y, bo.z, bo.w};
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int e = 4 * v + j;
-                                const float i_a = p_hard_sigmoid(__uint_as_float(gi[e]) + bis[j]);
-                                const float f_a = p_hard_sigmoid(__uint_as_float(gf[e]) + bfs[j]);
-                                const float o_a = p_hard_sigmoid(__uint_as_float(go[e]) + bos[j]);
-                                const float g_a = fmaxf(-1.f, fminf(1.f, __uint_as_float(gg[e]) + bgs[j]));
-                                const float c_new = __fmaf_rn(f_a, c[ch * 8 + e], __fmul_rn(i_a, g_a));
-                                c[ch * 8 + e] = c_new;
-                                const float h_new = o_a * p_tanh(c_new);
-                                packed[v] |= (uint32_t(p_quant_h(h_new)) & 0xFFu) << (8 * j);
-                            }
+                            const int e = 4 * v;
+                            const uint32_t lo = lstm_cell_pair(gi[e], gi[e + 1], gf[e], gf[e + 1], gg[e], gg[e + 1], go[e], go[e + 1],
+                                                               make_float2(bi.x, bi.y), make_float2(bf.x, bf.y),
+                                                               make_float2(bg.x, bg.y), make_float2(bo.x, bo.y), c2[(u >> 1)]);
+                            const uint32_t hi = lstm_cell_pair(gi[e + 2], gi[e + 3], gf[e + 2], gf[e + 3], gg[e + 2], gg[e + 3],
+                                                               go[e + 2], go[e + 3], make_float2(bi.z, bi.w), make_float2(bf.z, bf.w),
+                                                               make_float2(bg.z, bg.w), make_float2(bo.z, bo.w), c2[(u >> 1) + 1]);
+                            packed[v] = lo | (hi << 16);
                         }
                         if (row_ok) *reinterpret_cast<uint2 *>(hrow + ch * 8) = make_uint2(packed[0], packed[1]);
                     }
@@ -380,7 +404,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
 #pragma unroll
                     for (int v = 0; v < UNITS / 4; ++v)
                         *reinterpret_cast<float4 *>(p.c + int64_t(row) * p.H + n0 + 4 * v) =
-                            make_float4(c[4 * v], c[4 * v + 1], c[4 * v + 2], c[4 * v + 3]);
+                            make_float4(c2[2 * v].x, c2[2 * v].y, c2[2 * v + 1].x, c2[2 * v + 1].y);
                 }
             }
         }

@@ -298,8 +298,15 @@ extern "C" int fluke_sm100_lstm_step(const fluke_sm100_lstm_step_t *s, void *str
 
 extern "C" int fluke_sm100_lstm_layer_persistent(const void *layer, const void *x_down, void *hh_down,
                                                  void *flags, void *stream);
+extern "C" int fluke_sm100_lstm_layer_cluster(const void *layer, const void *x_down, int allow_waves,
+                                              void *stream);
+// 0: two launches per timestep; 1: the fastest single-launch form the shape and device allow
+// (cluster exchange while all row tiles of the layer fit on the device at once, else L2
+// exchange); 2: the L2-exchange form only.
+static int g_lstm_last_form = -1;  // form the last whole-layer call used: 0, 1 (cluster) or 2 (L2)
+extern "C" int fluke_sm100_lstm_last_form(void) { return g_lstm_last_form; }
 static int g_lstm_persistent = 1;
-extern "C" void fluke_sm100_set_lstm_persistent(int enabled) { g_lstm_persistent = enabled ? 1 : 0; }
+extern "C" void fluke_sm100_set_lstm_persistent(int mode) { g_lstm_persistent = mode < 0 ? 0 : (mode > 2 ? 1 : mode); }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -347,7 +354,17 @@ extern "C" int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, 
     // 2. the recurrence in persistent launches where the shape allows it
     if (phase_mask == 7 && g_lstm_persistent) {
         void *flags = ws + align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024);
-        rc = fluke_sm100_lstm_layer_persistent(l, x_down, hh_down, flags, stream);
+        // cluster exchange when all row tiles run at once; else L2 exchange; else clusters in rounds
+        rc = g_lstm_persistent == 1 ? fluke_sm100_lstm_layer_cluster(l, x_down, 0, stream) : -2;
+        g_lstm_last_form = 1;
+        if (rc == -2) {
+            rc = fluke_sm100_lstm_layer_persistent(l, x_down, hh_down, flags, stream);
+            g_lstm_last_form = 2;
+        }
+        if (rc == -2 && g_lstm_persistent == 1) {
+            rc = fluke_sm100_lstm_layer_cluster(l, x_down, 1, stream);
+            g_lstm_last_form = 1;
+        }
         if (rc == 0) {
             const int t_last = l->reverse ? 0 : T - 1;
             return (int)cudaMemcpyAsync(l->h_i8, static_cast<int8_t *>(l->h_out_i8) + size_t(t_last) * B * H,
@@ -356,6 +373,7 @@ extern "C" int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, 
         if (rc != -2) return rc;
     }
 
+    if (phase_mask == 7) g_lstm_last_form = 0;
     // 3. otherwise: plans of the per-step kernels (tensor maps built once; t is a plane coordinate)
     GemmPlan dp_first, dp_rest;
     {

@@ -56,10 +56,10 @@ inline int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, uint32_t elem_by
 }
 
 // Row-major 3-D tensor [planes, rows, cols]; boxes are 1 x box_rows x box_cols.
-inline int make_tmap_3d(CUtensorMap *m, CUtensorMapDataType dt, const void *base, uint64_t planes,
-                        uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
-                        uint64_t plane_stride_bytes, uint32_t box_rows, uint32_t box_cols,
-                        bool swizzle128) {
+inline int make_tmap_3d_sw(CUtensorMap *m, CUtensorMapDataType dt, const void *base, uint64_t planes,
+                           uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                           uint64_t plane_stride_bytes, uint32_t box_rows, uint32_t box_cols,
+                           CUtensorMapSwizzle swizzle) {
     encode_tiled_fn fn = get_encode_tiled();
     if (!fn) return (int)cudaErrorNotSupported;
     if ((reinterpret_cast<uintptr_t>(base) & 15u) || (row_stride_bytes & 15u) ||
@@ -70,10 +70,18 @@ inline int make_tmap_3d(CUtensorMap *m, CUtensorMapDataType dt, const void *base
     cuuint32_t box[3] = {box_cols, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(m, dt, 3, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+inline int make_tmap_3d(CUtensorMap *m, CUtensorMapDataType dt, const void *base, uint64_t planes,
+                        uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                        uint64_t plane_stride_bytes, uint32_t box_rows, uint32_t box_cols,
+                        bool swizzle128) {
+    return make_tmap_3d_sw(m, dt, base, planes, rows, cols, row_stride_bytes, plane_stride_bytes,
+                           box_rows, box_cols,
+                           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 }  // namespace fluke_sm100

@@ -376,12 +376,17 @@ typedef struct {
 size_t fluke_factored_lstm_layer_workspace(int T, int B, int H, int R);
 int fluke_factored_lstm_layer_i8_gpu(const fluke_flstm_layer_t *layer);
 
-/* How fluke_factored_lstm_layer_i8_gpu runs the recurrence: 1 (default) = one persistent launch
- * per layer with the gate weights in shared memory and the cell state in registers for all T
- * timesteps, when the shape is covered (R = 128, H a multiple of 128 up to 1024) and the device
- * can co-schedule its CTAs; 0 = always two launches per timestep. Both give the same int8
- * outputs within one code (the two K halves are accumulated in a different order). */
-void fluke_set_lstm_persistent(int enabled);
+/* How fluke_factored_lstm_layer_i8_gpu runs the recurrence.
+ *   1 (default): one launch per layer, gate weights in shared memory and the cell state in
+ *      registers for all T timesteps. Where the shape allows (R = 128, H a multiple of 64 up to
+ *      768) and the device can hold one cluster of H/64 + 4 thread blocks per 128-chunk row tile
+ *      at once (7 tiles on a B200), h / hh_down are exchanged through distributed shared memory;
+ *      otherwise (R = 128, H a multiple of 128 up to 1024) through L2 with per-tile counters.
+ *   2: the L2-exchange form only.
+ *   0: always two launches per timestep.
+ * All give the same int8 outputs within one code (the two K halves are accumulated in a
+ * different order). */
+void fluke_set_lstm_persistent(int mode);
 
 /* Measurement aid: launch only some kernel classes of the layer so one class can be timed
  * alone. phase_mask bits: 1 = x_down GEMM, 2 = per-step down-projection, 4 = per-step fused

@@ -51,4 +51,4 @@ int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int p
     return fluke_host_note_error(fluke_sm100_lstm_layer_phases(layer, phase_mask, fluke_host_stream()));
 }
 
-void fluke_set_lstm_persistent(int enabled) { fluke_sm100_set_lstm_persistent(enabled); }
+void fluke_set_lstm_persistent(int mode) { fluke_sm100_set_lstm_persistent(mode); }

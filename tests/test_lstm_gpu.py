@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from fluke_b200 import ops, prep
+from fluke_b200 import lib as L, ops, prep
 from fluke_b200.lstm import FactoredLstmLayer, run_stack
 from fluke_b200.shard import shard_range
 from oracle import port
@@ -18,10 +18,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=["persistent", "per_step"])
+LSTM_MODES = {"cluster": 1, "persistent_l2": 2, "per_step": 0}
+
+
+@pytest.fixture(params=list(LSTM_MODES))
 def lstm_mode(request, flib):
-    """Runs a test once with the persistent layer kernel and once with two launches per step."""
-    flib.fluke_set_lstm_persistent(1 if request.param == "persistent" else 0)
+    """Runs a test with each form of the layer recurrence: one launch with the exchange inside
+    thread-block clusters (the default where the shape allows it), one launch with the exchange
+    through L2, and two launches per step."""
+    flib.fluke_set_lstm_persistent(LSTM_MODES[request.param])
     yield request.param
     flib.fluke_set_lstm_persistent(1)
 
@@ -91,6 +96,7 @@ def test_layer_vs_oracle(T, B, reverse, lstm_mode):
     c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
     ho = ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale,
                                     layer.w_up, layer.bias, c, h, reverse=reverse)
+    assert L.load().fluke_sm100_lstm_last_form() == LSTM_MODES[lstm_mode]  # each form covers this shape
     he, ce, hf = _run_oracle_layer(layer, x, xs, reverse)
     d = np.abs(ho.cpu().numpy().astype(np.int32) - he.astype(np.int32))
     assert d.max() <= 1 and (d != 0).mean() < 5e-3
@@ -142,24 +148,42 @@ def test_stack_alternating_directions_and_batch_shards(lstm_mode):
 
 
 def test_persistent_and_per_step_layers_agree(flib):
-    """Same layer through both drivers: the only difference is the accumulation order of the two
+    """Same layer through all three drivers: the only difference is the accumulation order of the two
     K halves, so codes differ by at most one, rarely. Also a hidden size of 1024 (64 units per CTA)
     and a batch that is not a multiple of the 128-row tile."""
     for (T, B, H) in [(16, 300, 768), (6, 130, 1024), (5, 1024, 768)]:
         layer, x, xs = _layer_case(T, B, H, 128, 11 + B, False)
         outs = []
-        for mode in (1, 0):
+        for mode in (1, 2, 0):
             flib.fluke_set_lstm_persistent(mode)
             c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
             outs.append((ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh,
                                                     layer.dn_hh_scale, layer.w_up, layer.bias, c, h).clone(), c, h))
         flib.fluke_set_lstm_persistent(1)
-        d = (outs[0][0].int() - outs[1][0].int()).abs()
-        assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 5e-3
-        assert float((outs[0][1] - outs[1][1]).abs().max()) < 1e-2
+        for other in (outs[1], outs[2]):
+            d = (outs[0][0].int() - other[0].int()).abs()
+            assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 5e-3
+            assert float((outs[0][1] - other[1]).abs().max()) < 1e-2
+            assert torch.equal(outs[0][2], outs[0][0][-1]) and torch.equal(other[2], other[0][-1])
         he, ce, _ = _run_oracle_layer(layer, x, xs, False)
         d = np.abs(outs[0][0].cpu().numpy().astype(np.int32) - he.astype(np.int32))
         assert d.max() <= 1 and (d != 0).mean() < 5e-3
+
+
+def test_cluster_form_runs_in_rounds_when_nothing_else_covers_the_shape(flib):
+    """H = 192 is outside the L2-exchange form (H % 128) and 17 row tiles are more clusters than
+    fit at once, so the cluster form runs them in rounds; a ragged last tile as well."""
+    T, B, H, R = 4, 2100, 192, 128
+    layer, x, xs = _layer_case(T, B, H, R, 5, True)
+    c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
+    flib.fluke_set_lstm_persistent(1)
+    ho = ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale,
+                                    layer.w_up, layer.bias, c, h, reverse=True)
+    assert flib.fluke_sm100_lstm_last_form() == 1
+    he, ce, _ = _run_oracle_layer(layer, x, xs, True)
+    d = np.abs(ho.cpu().numpy().astype(np.int32) - he.astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() < 5e-3
+    assert np.abs(c.cpu().numpy() - ce).max() < 1e-2
 
 
 def test_layer_config_size_properties(lstm_mode):
@@ -172,6 +196,9 @@ def test_layer_config_size_properties(lstm_mode):
     args = (layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale, layer.w_up, layer.bias)
     c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
     fwd = ops.factored_lstm_layer_i8(X, XS, *args, c, h, reverse=False).clone()
+    # 8 row tiles are more than the clusters a B200 holds at once (7), so mode 1 picks the L2 form
+    form = L.load().fluke_sm100_lstm_last_form()
+    assert form == (2 if lstm_mode == "cluster" else LSTM_MODES[lstm_mode])
     assert int(fwd.min()) >= -127
     c2 = torch.zeros(B, H, device=DEV); h2 = torch.zeros(B, H, dtype=torch.int8, device=DEV)
     rev = ops.factored_lstm_layer_i8(X.flip(0).contiguous(), XS.view(T, B).flip(0).contiguous().view(-1), *args, c2, h2, reverse=True)
