@@ -9,9 +9,10 @@ path). One "step" = one pass of the whole stack over one [T, B, 768] int8 batch.
 
     value            chunk-timesteps per second per layer, summed over GPUs
                      = n_gpus * B * T * layers / step_time   (inputs resident in HBM)
-    e2e              the same through the public API with HOST buffers: pinned-host -> device
-                     copy of the step's input and device -> host copy of its output inside
-                     the timed region
+    e2e              the same through the public API with HOST buffers (fluke_b200.lstm.StackPipeline):
+                     every step copies its input from pinned host memory and its output back,
+                     all inside the timed region; the driver overlaps the copies of neighbouring
+                     steps with the layers of the current one (pipeline fill and drain included)
     roofline         the persistent LSTM recurrence kernel (tensor bound): algorithmic FLOPs per
                      launch / its launch duration, measured with CUDA events on the launching
                      stream, against the measured bf16 GEMM peak of this pool
@@ -249,7 +250,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from fluke_b200 import lib as flib, ops, prep
-    from fluke_b200.lstm import FactoredLstmLayer, run_stack
+    from fluke_b200.lstm import FactoredLstmLayer, StackPipeline, run_stack
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -286,24 +287,27 @@ def run_ours(args):
     def step_resident():
         return run_stack(layers, x_dev, xs_dev, state=fresh_state(), workspace=ws, buffers=bufs)[0]
 
+    # end to end: every pass copies its input from pinned host memory and its output back; the
+    # passes go through the library's streaming driver, which overlaps the copies of neighbouring
+    # passes with the layers of the current one
+    pipe = StackPipeline(layers, T, B, dev)
+
     def step_e2e():
-        xd = x_dev.copy_(x_host, non_blocking=True)
-        sd = xs_dev.copy_(xs_host, non_blocking=True)
-        y = run_stack(layers, xd, sd, state=fresh_state(), workspace=ws, buffers=bufs)[0]
-        out_host.copy_(y, non_blocking=True)
-        return y
+        return pipe.submit(x_host, xs_host, out_host)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, after=None):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
+        if after is not None:
+            after()
         e1.record()
         barrier()
         return reduce_step_time(e0.elapsed_time(e1) / steps)
@@ -316,7 +320,8 @@ def run_ours(args):
     ms = timed(step_resident, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+    pipe.drain()
+    ms_e2e = timed(step_e2e, args.steps, after=pipe.drain)   # fill and drain of the pipeline included
     status = flib.read_status()
     if status != 0:
         raise SystemExit(f"bench.py: device status word {status:#x}: a bounded device wait gave up")

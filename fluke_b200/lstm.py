@@ -64,3 +64,87 @@ def run_stack(layers, x_i8, x_scale, state=None, workspace=None, buffers=None):
                                    reverse=layer.reverse, h_out=out, workspace=workspace)
         cur, cur_scale = out, None
     return cur, state
+
+
+class StackPipeline:
+    """Host-to-host streaming of whole stack passes: while pass k runs the layers on the compute
+    stream, the input of pass k+1 is copied in and the output of pass k-1 is copied out on two
+    copy streams (the two PCIe directions are independent), so in steady state a pass costs
+    max(compute, copy-in, copy-out) instead of their sum.
+
+    Device memory: two input sets, the two ping-pong layer buffers and two output buffers of
+    [T,B,H] int8. Inputs and outputs are pinned host tensors; `submit` only enqueues work."""
+
+    def __init__(self, layers, T, B, device):
+        self.layers = layers
+        h = layers[0].hidden
+        self.shape = (T, B, h)
+        dev = torch.device(device)
+        self.device = dev
+        mk = lambda: torch.empty(T, B, h, dtype=torch.int8, device=dev)
+        self.x = [mk(), mk()]
+        self.xs = [torch.empty(T * B, dtype=torch.float32, device=dev) for _ in range(2)]
+        self.bufs = [mk(), mk()]
+        self.out = [mk(), mk()]
+        self.state = [[(torch.zeros(B, h, dtype=torch.float32, device=dev),
+                        torch.zeros(B, h, dtype=torch.int8, device=dev)) for _ in layers] for _ in range(2)]
+        need = ops._L().fluke_factored_lstm_layer_workspace(T, B, h, layers[0].rank)
+        self.ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]     # input set k%2 copied in
+        self.ev_run = [torch.cuda.Event() for _ in range(2)]    # pass that used slot k%2 finished computing
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]    # output buffer k%2 copied out
+        self.k = 0
+
+    def submit(self, x_host, xs_host, out_host, zero_state=True):
+        """Enqueue one pass: x_host int8 [T,B,H] and xs_host f32 [T*B] (pinned) in, the last layer's
+        int8 output into out_host (pinned). Returns the event that marks out_host complete."""
+        k, slot = self.k, self.k % 2
+        self.k += 1
+        cur = torch.cuda.current_stream(self.device)
+        # copy-in: the slot's previous pass (k-2) must have finished reading it
+        self.s_in.wait_stream(cur)
+        if k >= 2:
+            self.s_in.wait_event(self.ev_run[slot])
+        with torch.cuda.stream(self.s_in):
+            self.x[slot].copy_(x_host, non_blocking=True)
+            self.xs[slot].copy_(xs_host, non_blocking=True)
+            self.ev_in[slot].record()
+        # compute: after its input is in, and after the copy-out that last read this output buffer
+        self.s_run.wait_event(self.ev_in[slot])
+        if k >= 2:
+            self.s_run.wait_event(self.ev_out[slot])
+        lib = ops._L()
+        prev_stream = lib.fluke_get_stream()
+        lib.fluke_set_stream(self.s_run.cuda_stream)
+        try:
+            with torch.cuda.stream(self.s_run):
+                if zero_state:
+                    for c, hs in self.state[slot]:
+                        c.zero_()
+                        hs.zero_()
+                cur_x, cur_s = self.x[slot], self.xs[slot]
+                n = len(self.layers)
+                for i, layer in enumerate(self.layers):
+                    c, hs = self.state[slot][i]
+                    dst = self.out[slot] if i == n - 1 else self.bufs[i % 2]
+                    ops.factored_lstm_layer_i8(cur_x, cur_s, layer.dn_ih, layer.dn_ih_scale, layer.dn_hh,
+                                               layer.dn_hh_scale, layer.w_up, layer.bias, c, hs,
+                                               reverse=layer.reverse, h_out=dst, workspace=self.ws)
+                    cur_x, cur_s = dst, None
+                self.ev_run[slot].record()
+        finally:
+            lib.fluke_set_stream(prev_stream)
+        # copy-out
+        self.s_out.wait_event(self.ev_run[slot])
+        with torch.cuda.stream(self.s_out):
+            out_host.copy_(self.out[slot], non_blocking=True)
+            self.ev_out[slot].record()
+        return self.ev_out[slot]
+
+    def drain(self):
+        """Make the current stream wait for everything submitted so far."""
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_stream(self.s_in)
+        cur.wait_stream(self.s_run)
+        cur.wait_stream(self.s_out)

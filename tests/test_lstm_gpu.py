@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from fluke_b200 import lib as L, ops, prep
-from fluke_b200.lstm import FactoredLstmLayer, run_stack
+from fluke_b200.lstm import FactoredLstmLayer, StackPipeline, run_stack
 from fluke_b200.shard import shard_range
 from oracle import port
 
@@ -211,3 +211,24 @@ def test_layer_config_size_properties(lstm_mode):
     assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 1e-3
     if lstm_mode == "per_step":
         assert torch.equal(h3, fwd[0])
+
+
+def test_streaming_pipeline_equals_pass_by_pass():
+    """Four passes with different inputs through the three-stream driver (copy-in, layers,
+    copy-out overlapped across passes) give the bytes of run_stack on each input alone."""
+    T, B, H, R, NL = 6, 200, 768, 128, 3
+    g = torch.Generator().manual_seed(77)
+    layers = [FactoredLstmLayer.random(H, R, bool(i % 2), g, DEV) for i in range(NL)]
+    pipe = StackPipeline(layers, T, B, DEV)
+    ins, outs = [], []
+    for k in range(4):
+        x, xs = prep.quantize_int8_rows(torch.randn(T * B, H, generator=g))
+        ins.append((x.view(T, B, H).contiguous().pin_memory(), xs.contiguous().pin_memory()))
+        outs.append(torch.empty(T, B, H, dtype=torch.int8).pin_memory())
+    for k in range(4):
+        pipe.submit(ins[k][0], ins[k][1], outs[k])
+    pipe.drain()
+    torch.cuda.synchronize()
+    for k in range(4):
+        ref, _ = run_stack(layers, ins[k][0].to(DEV), ins[k][1].to(DEV))
+        assert torch.equal(outs[k], ref.cpu())
