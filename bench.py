@@ -360,7 +360,11 @@ def run_ours(args):
         achieved = flops / (per_kernel[kname] * 1e-6) / 1e12
         roofline = {"kernel": kname, "bound": "tensor", "achieved": round(achieved, 2),
                     "peak": peaks["tf_sustained"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tf_sustained"], 4),
-                    "peak_source": f"{peaks['source']} bf16 GEMM, sustained", "traffic": None,
+                    "peak_source": f"{peaks['source']} bf16 GEMM, sustained",
+                    # DRAM bytes per launch: ncu capture of this kernel at T = 24 (0.5 MB read per
+                    # step) scaled to T steps, plus the h_out it writes (larger than L2)
+                    "traffic": (0.5e6 * T + float(T) * B * H) if form == 2 else None,
+                    "traffic_source": "ncu dram bytes at T=24 scaled by T, plus h_out writes" if form == 2 else None,
                     "flops_per_launch": flops, "us_per_launch": {k: round(v, 3) for k, v in per_kernel.items()}}
         cpu_v, cores, sample = cpu_lstm_sample()
         ops_res = bench_ops(torch, peaks)
