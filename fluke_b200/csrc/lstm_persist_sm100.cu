@@ -183,8 +183,9 @@ __device__ __forceinline__ uint32_t lstm_cell_pair(uint32_t gi0, uint32_t gi1, u
     const float2 th = add2(make_float2(1.f, 1.f), make_float2(-q.x, -q.y));
     const float2 hs = mul2(mul2(o_a, th), make_float2(127.f, 127.f));
     // round half away from zero: add 0.5 with the sign of the value, then truncate
-    const float hx = hs.x + __uint_as_float(0x3F000000u | (__float_as_uint(hs.x) & 0x80000000u));
-    const float hy = hs.y + __uint_as_float(0x3F000000u | (__float_as_uint(hs.y) & 0x80000000u));
+    // (__fadd_rn: never fused with the multiplication before it)
+    const float hx = __fadd_rn(hs.x, __uint_as_float(0x3F000000u | (__float_as_uint(hs.x) & 0x80000000u)));
+    const float hy = __fadd_rn(hs.y, __uint_as_float(0x3F000000u | (__float_as_uint(hs.y) & 0x80000000u)));
     return (uint32_t(__float2int_rz(hx)) & 0xFFu) | ((uint32_t(__float2int_rz(hy)) & 0xFFu) << 8);
 }
 

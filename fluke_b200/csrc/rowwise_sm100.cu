@@ -16,6 +16,7 @@
 // (e0 [+ e2]) + (e1 [+ e3]) over the q index followed by lane distances 16 and 8.
 // Other reductions of the path are maxima, which do not depend on order.
 #include "fluke_sm100.h"
+#include "sm100_ptx.cuh"
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -87,6 +88,24 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 __device__ __forceinline__ int clamp127(int v) { return max(-127, min(127, v)); }
 
+// int8 <-> f32 without the conversion unit (a quarter-rate pipe that the int8 RMSNorm kernel would
+// otherwise keep 60 % busy).
+// Byte j of `biased` (= the int8 bytes with their sign bits flipped, i.e. value + 128 as
+// unsigned) becomes the low mantissa byte of 2^23; subtracting 2^23 + 128 leaves the value.
+__device__ __forceinline__ float2 i8_pair_to_float(uint32_t biased, uint32_t sel_lo, uint32_t sel_hi) {
+    const float a = __uint_as_float(__byte_perm(biased, 0x4B000000u, sel_lo));
+    const float b = __uint_as_float(__byte_perm(biased, 0x4B000000u, sel_hi));
+    return make_float2(__fadd_rn(a, -8388736.0f), __fadd_rn(b, -8388736.0f));
+}
+// Round-to-nearest-even integer of v (|v| < 2^22) in the low bits of the result: adding
+// 1.5 * 2^23 leaves the integer, in two's complement, in the low mantissa bits. (__fadd_rn: the
+// addition must not be fused with the multiplication that produced v.)
+__device__ __forceinline__ uint32_t round_to_int_bits(float v) { return __float_as_uint(__fadd_rn(v, 12582912.0f)); }
+// The low bytes of four words, packed.
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
 // Sum of squares of one row in the reference's summation order. `sq[q][k]` is the
 // x*x + y*y term of pair k of this lane's chunk in load q; L = hidden_dim / 256.
 template <int L>
@@ -141,21 +160,22 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
                         static_cast<const __half *>(residual_in) + base + off)), rf);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                val[q][k] = make_float2(xf[k].x + rf[k].x * alpha, xf[k].y + rf[k].y * alpha);
+                val[q][k] = fma2(rf[k], make_float2(alpha, alpha), xf[k]);
         } else {
             const uint2 raw = *reinterpret_cast<const uint2 *>(
                 static_cast<const uint8_t *>(residual_in) + base + off);
             const uint8_t *rb = reinterpret_cast<const uint8_t *>(&raw);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                float r0, r1;
                 if constexpr (MODE == kOutI8) {
-                    r0 = (float)(int8_t)rb[2 * k];
-                    r1 = (float)(int8_t)rb[2 * k + 1];
-                    val[q][k] = make_float2(xf[k].x + (r0 * rs) * alpha, xf[k].y + (r1 * rs) * alpha);
+                    const uint32_t word = ((k < 2) ? raw.x : raw.y) ^ 0x80808080u;
+                    const float2 r = i8_pair_to_float(word, 0x7440u + 2 * (k & 1), 0x7441u + 2 * (k & 1));
+                    // x + (r * rs) * alpha: product, then one fused multiply-add (the form the
+                    // reference's build contracts to), two elements per instruction
+                    val[q][k] = fma2(mul2(r, make_float2(rs, rs)), make_float2(alpha, alpha), xf[k]);
                 } else {
-                    r0 = e4m3_decode(rb[2 * k]);
-                    r1 = e4m3_decode(rb[2 * k + 1]);
+                    const float r0 = e4m3_decode(rb[2 * k]);
+                    const float r1 = e4m3_decode(rb[2 * k + 1]);
                     val[q][k] = make_float2(xf[k].x + r0 * rs * alpha, xf[k].y + r1 * rs * alpha);
                 }
             }
@@ -175,7 +195,7 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
         unpack8(__ldg(reinterpret_cast<const uint4 *>(weight + off)), wf);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            val[q][k] = make_float2(val[q][k].x * rms_inv * wf[k].x, val[q][k].y * rms_inv * wf[k].y);
+            val[q][k] = mul2(mul2(val[q][k], make_float2(rms_inv, rms_inv)), wf[k]);
             amax = fmaxf(amax, fmaxf(fabsf(val[q][k].x), fabsf(val[q][k].y)));
         }
         if constexpr (MODE == kOutF16)
@@ -190,13 +210,20 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
 #pragma unroll
         for (int q = 0; q < L; ++q) {
             const int off = (q * 32 + lane) * 8;
-            uint2 raw;
-            int8_t *ob = reinterpret_cast<int8_t *>(&raw);
+            // |val * quant_scale| <= 127 (1 + 2^-23) by construction of the scale, so the rounded
+            // integer needs no clamp (NaN inputs, which the reference maps to 0, give -1 here)
+            uint32_t t[8];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                ob[2 * k] = (int8_t)clamp127(__float2int_rn(val[q][k].x * quant_scale));
-                ob[2 * k + 1] = (int8_t)clamp127(__float2int_rn(val[q][k].y * quant_scale));
+                // the product is rounded to f32 first, then p * 1 + 1.5 * 2^23 rounds it to an
+                // integer (a packed multiply followed by a packed add was observed to come out
+                // as ONE fused operation, which rounds only once)
+                const float2 rq = fma2(mul2(val[q][k], make_float2(quant_scale, quant_scale)),
+                                       make_float2(1.0f, 1.0f), make_float2(12582912.0f, 12582912.0f));
+                t[2 * k] = __float_as_uint(rq.x);
+                t[2 * k + 1] = __float_as_uint(rq.y);
             }
+            const uint2 raw = make_uint2(pack_low_bytes(t[0], t[1], t[2], t[3]), pack_low_bytes(t[4], t[5], t[6], t[7]));
             *reinterpret_cast<uint2 *>(static_cast<uint8_t *>(out) + base + off) = raw;
         }
     } else {
@@ -395,18 +422,34 @@ quant_rows_kernel(const __half *__restrict__ in, uint8_t *__restrict__ out,
 // the same order is spelled out with intrinsics here so it does not depend on the compiler.
 // Vector path: one thread rotates 8 pairs (x0 = 16 bytes at offset 8c, x1 = 16 bytes at offset
 // W + 8c). With 8 heads of 64 and W = 32 a warp covers one (batch, position) row of 1 KB.
+// SHIFTS: the thread index decomposes with shifts and one 32-bit division (chunks per head and
+// heads both powers of two, fewer than 2^31 threads); otherwise with 64-bit divisions, which cost
+// more instructions than the rotation itself.
+template <bool SHIFTS>
 __global__ void __launch_bounds__(256)
 rotary_vec_kernel(__half *x, const float *__restrict__ sin_tab, const float *__restrict__ cos_tab,
                   int64_t total, int seq_len, int n_heads, int width, int64_t stride_batch,
-                  int64_t stride_seq, int64_t stride_head) {
+                  int64_t stride_seq, int64_t stride_head, int cpw_log2, int heads_log2) {
     const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total) return;
-    const int cpw = width >> 3;
-    const int c = int(idx % cpw);
-    int64_t r = idx / cpw;
-    const int h = int(r % n_heads); r /= n_heads;
-    const int s = int(r % seq_len);
-    const int64_t b = r / seq_len;
+    int c, h, s;
+    int64_t b;
+    if constexpr (SHIFTS) {
+        const uint32_t i32 = uint32_t(idx);
+        c = int(i32 & ((1u << cpw_log2) - 1u));
+        h = int((i32 >> cpw_log2) & ((1u << heads_log2) - 1u));
+        const uint32_t row = i32 >> (cpw_log2 + heads_log2);
+        const uint32_t bq = row / uint32_t(seq_len);
+        s = int(row - bq * uint32_t(seq_len));
+        b = bq;
+    } else {
+        const int cpw = width >> 3;
+        c = int(idx % cpw);
+        int64_t r = idx / cpw;
+        h = int(r % n_heads); r /= n_heads;
+        s = int(r % seq_len);
+        b = r / seq_len;
+    }
 
     __half *p0 = x + b * stride_batch + s * stride_seq + h * stride_head + c * 8;
     __half *p1 = p0 + width;
@@ -676,10 +719,20 @@ extern "C" int fluke_sm100_rotary_emb(void *x, const void *sin_tab, const void *
                      (((reinterpret_cast<uintptr_t>(sin_tab) | reinterpret_cast<uintptr_t>(cos_tab)) & 15u) == 0);
     if (vec) {
         const int64_t total = int64_t(batch_size) * seq_len * n_heads * (W / 8);
-        rotary_vec_kernel<<<grid_for(total, 256), 256, 0, s>>>(
-            static_cast<__half *>(x), static_cast<const float *>(sin_tab),
-            static_cast<const float *>(cos_tab), total, seq_len, n_heads, W, stride_batch,
-            stride_seq, stride_head);
+        const int cpw = W / 8;
+        auto log2_of = [](int v) { int l = 0; while ((1 << l) < v) ++l; return (1 << l) == v ? l : -1; };
+        const int cl = log2_of(cpw), hl = log2_of(n_heads);
+        if (cl >= 0 && hl >= 0 && total < (int64_t(1) << 31)) {
+            rotary_vec_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(
+                static_cast<__half *>(x), static_cast<const float *>(sin_tab),
+                static_cast<const float *>(cos_tab), total, seq_len, n_heads, W, stride_batch,
+                stride_seq, stride_head, cl, hl);
+        } else {
+            rotary_vec_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(
+                static_cast<__half *>(x), static_cast<const float *>(sin_tab),
+                static_cast<const float *>(cos_tab), total, seq_len, n_heads, W, stride_batch,
+                stride_seq, stride_head, 0, 0);
+        }
     } else {
         const int64_t total = int64_t(batch_size) * seq_len * n_heads * W;
         rotary_scalar_kernel<<<grid_for(total, 256), 256, 0, s>>>(

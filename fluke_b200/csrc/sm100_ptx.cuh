@@ -298,17 +298,20 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 // Packed pairs of f32: one instruction per two IEEE round-to-nearest results (each half is
-// bit-identical to the scalar mul.rn / fma.rn).
+// bit-identical to the scalar add.rn / mul.rn / fma.rn). The rounding mode is spelled out: without
+// it the assembler may merge a multiplication with a following addition into one fused operation.
+// Even so, do not feed mul2 straight into add2 where the two roundings matter: that pair was
+// observed to behave as one fused multiply-add; write fma2(mul2(a, b), one, c) instead.
 __device__ __forceinline__ float2 add2(float2 a, float2 b) {
     float2 c;
-    asm("add.f32x2 %0, %1, %2;"
+    asm("add.rn.f32x2 %0, %1, %2;"
         : "=l"(reinterpret_cast<uint64_t &>(c))
         : "l"(reinterpret_cast<const uint64_t &>(a)), "l"(reinterpret_cast<const uint64_t &>(b)));
     return c;
 }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
     float2 c;
-    asm("mul.f32x2 %0, %1, %2;"
+    asm("mul.rn.f32x2 %0, %1, %2;"
         : "=l"(reinterpret_cast<uint64_t &>(c))
         : "l"(reinterpret_cast<const uint64_t &>(a)), "l"(reinterpret_cast<const uint64_t &>(b)));
     return c;

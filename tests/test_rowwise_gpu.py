@@ -118,7 +118,7 @@ def test_quantisers_side_by_side(n, h):
     assert torch.equal(q, q2) and same_bits(s, s2) and torch.equal(f, f2) and same_bits(fs, fs2)
 
 
-@pytest.mark.parametrize("b,s,h,w,hd", [(32, 1000, 8, 32, 64), (4, 128, 8, 32, 64), (3, 77, 8, 16, 64), (2, 5, 3, 5, 16)])
+@pytest.mark.parametrize("b,s,h,w,hd", [(32, 1000, 8, 32, 64), (4, 128, 8, 32, 64), (3, 77, 8, 16, 64), (2, 5, 3, 5, 16), (2, 50, 6, 32, 64), (5, 33, 4, 24, 64)])
 def test_rotary_side_by_side(b, s, h, w, hd):
     R = _ref()
     g = torch.Generator().manual_seed(b * s)
