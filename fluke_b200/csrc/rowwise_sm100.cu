@@ -108,6 +108,45 @@ __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint3
 
 // Sum of squares of one row in the reference's summation order. `sq[q][k]` is the
 // x*x + y*y term of pair k of this lane's chunk in load q; L = hidden_dim / 256.
+// L = 2 with half the shuffles: instead of every lane of an 8-lane group reducing all eight
+// (q, k) terms redundantly, each butterfly step also halves the set a lane is responsible for
+// (the partner receives the other half), so after the three steps lane bits (2, 1, 0) select
+// which one of the eight group sums the lane holds: k = 2 * bit2 + bit1, q = bit0. The additions
+// are the same pairs in the same order as in the plain form, and a + b == b + a, so every lane
+// ends with the same bits as before.
+__device__ __forceinline__ float row_sum_sq_2(const float (&sq)[2][4], int lane) {
+    const bool b2 = lane & 4, b1 = lane & 2, b0 = lane & 1;
+    // lane distance 4: keep k in {0,1} (bit2 = 0) or {2,3} (bit2 = 1), for both q
+    float a[2][2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float keep = b2 ? sq[q][2 + j] : sq[q][j];
+            const float send = b2 ? sq[q][j] : sq[q][2 + j];
+            a[q][j] = keep + __shfl_xor_sync(kFull, send, 4);
+        }
+    // lane distance 2: keep k's low bit = bit1
+    float c[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const float keep = b1 ? a[q][1] : a[q][0];
+        const float send = b1 ? a[q][0] : a[q][1];
+        c[q] = keep + __shfl_xor_sync(kFull, send, 2);
+    }
+    // lane distance 1: keep q = bit0
+    const float keep = b0 ? c[1] : c[0];
+    const float send = b0 ? c[0] : c[1];
+    float p = keep + __shfl_xor_sync(kFull, send, 1);   // the group's sum of term (q, k)
+    // e_q = (p0 + p2) + (p1 + p3), then e0 + e1: partners differ in bit2, bit1, bit0
+    p += __shfl_xor_sync(kFull, p, 4);
+    p += __shfl_xor_sync(kFull, p, 2);
+    p += __shfl_xor_sync(kFull, p, 1);
+    p += __shfl_xor_sync(kFull, p, 16);
+    p += __shfl_xor_sync(kFull, p, 8);
+    return p;
+}
+
 template <int L>
 __device__ __forceinline__ float row_sum_sq(const float (&sq)[L][4]) {
     float e[L];
@@ -184,8 +223,13 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
         for (int k = 0; k < 4; ++k) sq[q][k] = val[q][k].x * val[q][k].x + val[q][k].y * val[q][k].y;
     }
 
-    const float sum_sq = row_sum_sq<L>(sq);
-    const float rms_inv = rsqrtf(sum_sq / hidden_dim + eps);
+    float sum_sq;
+    if constexpr (L == 2) sum_sq = row_sum_sq_2(sq, lane);
+    else sum_sq = row_sum_sq<L>(sq);
+    // hidden_dim = 256 * L: for L a power of two the division is an exact scaling, done as a
+    // multiplication by the exact reciprocal (same bits, a few instructions fewer)
+    const float mean_sq = (L == 1 || L == 2 || L == 4) ? sum_sq * (1.0f / (256.0f * L)) : sum_sq / hidden_dim;
+    const float rms_inv = rsqrtf(mean_sq + eps);
 
     float amax = 0.f;
 #pragma unroll
