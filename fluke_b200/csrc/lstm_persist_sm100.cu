@@ -14,10 +14,15 @@
 //               as soon as its tile is there, the hh_down half when the projected hidden state
 //               arrives; gates, cell update and the int8 hidden slice follow, written to h_out[t]
 //               and published with a counter.
-//   worker CTAs (row tile) x (half of the R projection columns). The int8 down-projection
-//               weights stay in shared memory. Per step: wait until all slices of the tile have
-//               published h_{t-1}, TMA-load the tile, tcgen05 kind::i8 contraction, scale,
-//               round to f16 (as the two-kernel form does) and publish hh_down[tile].
+//   worker CTAs (row tile) x (half of the tile's ROWS). The int8 down-projection weights (all
+//               R rows) stay in shared memory. Per step: wait until all slices of the tile have
+//               published h_{t-1}, TMA-load the worker's 64 rows of it, tcgen05 kind::i8
+//               contraction, scale, round to f16 (as the two-kernel form does) and publish its
+//               rows of hh_down[tile]. The split is over rows, not projection columns, because
+//               the load of h is what the step waits for longest: a worker takes in 64 x H bytes
+//               instead of 128 x H. The MMA still has M = 128; the upper 64 rows of its A operand
+//               are whatever lies behind the valid rows in shared memory, and the accumulator
+//               rows they produce are never read.
 //
 // Exchange between CTAs goes through L2 (h_out itself and a [B,R] f16 buffer) with per-tile
 // counters: writers store, meet at a CTA-scope barrier, then one thread fences at GPU scope and
@@ -41,7 +46,7 @@ namespace fluke_sm100 {
 namespace {
 
 constexpr int kPThreads = 320;          // warp 0 producer, warp 1 MMA, warps 2-5 / 6-9 epilogue
-constexpr int kPWorkersPerTile = 2;     // each projects R/2 = 64 columns
+constexpr int kPWorkersPerTile = 2;     // each projects 64 of the tile's 128 rows
 constexpr int kPRank = 128;             // factor rank the kernel is built for
 constexpr int kPMaxHKB = 8;             // hidden K blocks of 128 bytes: H <= 1024
 constexpr int kPTmemCols = 256;
@@ -76,15 +81,18 @@ struct PersistSmem {
     static constexpr int kOffBias = kOffX + 2 * 32768;      // 4 x UNITS floats
     static constexpr int kGateBytes = kOffBias + 4 * UNITS * 4;
     // worker role
-    static constexpr int kDnKB = 64 * 128;                  // 64 projection rows x 128 B
+    static constexpr int kDnKB = kPRank * 128;              // R projection rows x 128 B
     static constexpr int kOffDn = 0;
     static constexpr int kOffH = kPMaxHKB * kDnKB;
-    static constexpr int kWorkerBytes = kOffH + kPMaxHKB * 16384;
+    static constexpr int kHKB = 64 * 128;                   // 64 rows of h x 128 B per K block
+    // the MMA reads 128 rows per K block: one more block of slack behind the last one
+    static constexpr int kWorkerBytes = kOffH + (kPMaxHKB + 1) * kHKB;
     static constexpr int kData = ((kGateBytes > kWorkerBytes ? kGateBytes : kWorkerBytes) + 15) / 16 * 16;
     static constexpr int kOffBars = kData;
-    static constexpr int kNumBars = 24;
+    static constexpr int kNumBars = 12;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kDynamic = kOffMisc + 16 + 1024;
+    static_assert(kDynamic <= 232448, "shared memory budget of one CTA exceeded");
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p) {
@@ -210,7 +218,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
     uint64_t *bar_x = &bars[5];          // [2] gate: x_down tile filled
     uint64_t *bar_ahh = &bars[7];        // [2] gate: hh_down tile filled
     uint64_t *bar_epi = &bars[9];        // [2] epilogue warps have stored their part of the step
-    uint64_t *bar_h = &bars[11];         // [kPMaxHKB] worker: h tile K block filled
+    uint64_t *bar_h = &bars[11];         // worker: its rows of the h tile filled
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kOffMisc + 4);
 
@@ -223,12 +231,12 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
         mbar_init(bar_once, 1);
         for (int g = 0; g < 2; ++g) {
             mbar_init(&bar_acc_full[g], 1);
-            mbar_init(&bar_acc_empty[g], is_gate ? 4 : 8);
+            mbar_init(&bar_acc_empty[g], 4);
             mbar_init(&bar_x[g], 1);
             mbar_init(&bar_ahh[g], 1);
-            mbar_init(&bar_epi[g], is_gate ? 4 : 8);
+            mbar_init(&bar_epi[g], 4);
         }
-        for (int i = 0; i < kPMaxHKB; ++i) mbar_init(&bar_h[i], 1);
+        mbar_init(bar_h, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -264,8 +272,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         if (!ok) break;
                         uint8_t *sx = smem + L::kOffX + g * 32768;
                         mbar_arrive_expect_tx(&bar_x[g], 32768);
-                        tma_load_3d(sx, &tm_x, &bar_x[g], 0, m0, time_of(i));
-                        tma_load_3d(sx + 16384, &tm_x, &bar_x[g], 64, m0, time_of(i));
+                        tma_load_4d(sx, &tm_x, &bar_x[g], 0, m0, 0, time_of(i));  // both K blocks
                     }
                     for (int g = 0; g < n_local && ok; ++g) {
                         const int tile = 2 * pair + g;
@@ -276,8 +283,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         fence_proxy_async_all();
                         uint8_t *sa = smem + L::kOffAhh + g * 32768;
                         mbar_arrive_expect_tx(&bar_ahh[g], 32768);
-                        tma_load_3d(sa, &tm_hh, &bar_ahh[g], 0, tile * 128, 0);
-                        tma_load_3d(sa + 16384, &tm_hh, &bar_ahh[g], 64, tile * 128, 0);
+                        tma_load_3d(sa, &tm_hh, &bar_ahh[g], 0, tile * 128, 0);  // both K blocks
                     }
                 }
             }
@@ -411,8 +417,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
         }
     } else {
         const int tile = (blockIdx.x - n_gate) / kPWorkersPerTile;
-        const int r0 = ((blockIdx.x - n_gate) % kPWorkersPerTile) * 64;  // projection columns of this worker
-        const int m0 = tile * 128;
+        const int m0 = tile * 128 + ((blockIdx.x - n_gate) % kPWorkersPerTile) * 64;  // first row of this worker
         unsigned int *h_ready = p.flags + tile;
         unsigned int *hh_ready = p.flags + p.n_tiles + tile;
         if (warp == 0) {
@@ -420,7 +425,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar_once, p.nkb_h * L::kDnKB);
                 for (int kb = 0; kb < p.nkb_h; ++kb)
-                    tma_load_2d(smem + L::kOffDn + kb * L::kDnKB, &tm_dn, bar_once, kb * 128, r0);
+                    tma_load_2d(smem + L::kOffDn + kb * L::kDnKB, &tm_dn, bar_once, kb * 128, 0);
                 bool ok = true;
                 for (int i = 0; i < p.T && ok; ++i) {
                     if (i > 0) {
@@ -431,83 +436,93 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 4] = clock64();
                         fence_proxy_async_all();
                     }
-                    for (int kb = 0; kb < p.nkb_h; ++kb) {
-                        mbar_arrive_expect_tx(&bar_h[kb], 16384);
-                        if (i == 0) tma_load_3d(smem + L::kOffH + kb * 16384, &tm_h0, &bar_h[kb], kb * 128, m0, 0);
-                        else tma_load_3d(smem + L::kOffH + kb * 16384, &tm_h, &bar_h[kb], kb * 128, m0, time_of(i - 1));
-                    }
+                    // ONE instruction for the worker's rows of the whole tile: the map walks the K
+                    // blocks of a row as its third dimension, so they land block after block (several
+                    // smaller loads, which would let the contraction start earlier, measured slower)
+                    mbar_arrive_expect_tx(bar_h, p.nkb_h * L::kHKB);
+                    if (i == 0) tma_load_4d(smem + L::kOffH, &tm_h0, bar_h, 0, m0, 0, 0);
+                    else tma_load_4d(smem + L::kOffH, &tm_h, bar_h, 0, m0, 0, time_of(i - 1));
                 }
             }
             __syncwarp();
         } else if (warp == 1) {
             // ------------------------------ worker: MMA issuer --------------------------
-            constexpr uint32_t kIdesc = make_idesc<kKindI8>(128, 64);
-            bool ok = mbar_wait(bar_once, 0, abort_flag, 50);
-            for (int i = 0; i < p.T && ok; ++i) {
-                if (i > 0) ok = mbar_wait(&bar_acc_empty[0], (i - 1) & 1, abort_flag, 51);
-                for (int kb = 0; kb < p.nkb_h && ok; ++kb) {
-                    ok = mbar_wait(&bar_h[kb], i & 1, abort_flag, 52);
+            constexpr uint32_t kIdesc = make_idesc<kKindI8>(128, kPRank);
+            if (lane == 0) {
+                bool ok = mbar_wait(bar_once, 0, abort_flag, 50);
+                for (int i = 0; i < p.T && ok; ++i) {
+                    if (i > 0) ok = mbar_wait(&bar_acc_empty[0], (i - 1) & 1, abort_flag, 51);
+                    if (!ok) break;
+                    ok = mbar_wait(bar_h, i & 1, abort_flag, 52);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    if (lane == 0) {
-                        const uint64_t ad = make_smem_desc_sw128(smem_u32(smem + L::kOffH + kb * 16384));
+                    for (int kb = 0; kb < p.nkb_h; ++kb) {
+                        // rows 64-127 of the operand overlap the next K block (or the slack)
+                        const uint64_t ad = make_smem_desc_sw128(smem_u32(smem + L::kOffH + kb * L::kHKB));
                         const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffDn + kb * L::kDnKB));
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             tc_mma<kKindI8>(tmem_base, ad + uint64_t(2 * k), bd + uint64_t(2 * k), kIdesc,
                                             (kb | k) != 0 ? 1u : 0u);
-                        if (kb == p.nkb_h - 1) tc_commit(&bar_acc_full[0]);
                     }
-                    __syncwarp();
+                    tc_commit(&bar_acc_full[0]);
                 }
             }
+            __syncwarp();
         } else {
             // ------------------------------ worker: epilogue ----------------------------
+            // The valid accumulator rows are TMEM lanes 0-63: only the warps of lane quadrants 0
+            // and 1 take part (two per quadrant, 64 projection columns each).
             const int q = warp & 3;
-            const int chalf = (warp - 2) >> 2;
-            const int row = m0 + q * 32 + lane;
-            const bool row_ok = row < p.B;
-            const int col0 = r0 + chalf * 32;
-            float sc[32];
+            if (q < 2) {
+                const int chalf = (warp - 2) >> 2;
+                const int row = m0 + q * 32 + lane;
+                const bool row_ok = row < p.B;
+                const int col0 = chalf * 64;
+                float sc[64];
 #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-                const float4 s4 = __ldg(reinterpret_cast<const float4 *>(p.dn_scale + col0) + v);
-                // same operand order as the dequant GEMM epilogue: sa * sb
-                sc[4 * v] = (1.0f / 127.0f) * s4.x; sc[4 * v + 1] = (1.0f / 127.0f) * s4.y;
-                sc[4 * v + 2] = (1.0f / 127.0f) * s4.z; sc[4 * v + 3] = (1.0f / 127.0f) * s4.w;
-            }
-            const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + chalf * 32;
-            __half *orow = p.hh_down + int64_t(row) * kPRank + col0;
-            bool ok = true;
-            for (int i = 0; i < p.T && ok; ++i) {
-                ok = mbar_wait(&bar_acc_full[0], i & 1, abort_flag, 53);
-                if (!ok) break;
-                if (p.trace && int(blockIdx.x) == n_gate && threadIdx.x == 64) p.trace[i * 8 + 5] = clock64();
-                tc_fence_after_sync();
-                uint32_t acc[32];
-                tmem_ld_32x32(t_row, acc);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_acc_empty[0]);
-                if (row_ok) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int e = 8 * v + 2 * j;
-                            const __half2 h2 = __floats2half2_rn(float(int(acc[e])) * sc[e],
-                                                                 float(int(acc[e + 1])) * sc[e + 1]);
-                            w[j] = *reinterpret_cast<const uint32_t *>(&h2);
-                        }
-                        *reinterpret_cast<uint4 *>(orow + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
+                for (int v = 0; v < 16; ++v) {
+                    const float4 s4 = __ldg(reinterpret_cast<const float4 *>(p.dn_scale + col0) + v);
+                    // same operand order as the dequant GEMM epilogue: sa * sb
+                    sc[4 * v] = (1.0f / 127.0f) * s4.x; sc[4 * v + 1] = (1.0f / 127.0f) * s4.y;
+                    sc[4 * v + 2] = (1.0f / 127.0f) * s4.z; sc[4 * v + 3] = (1.0f / 127.0f) * s4.w;
                 }
-                ok = warps_barrier(&bar_epi[0], i & 1, lane, abort_flag);
-                if (ok && warp == 2 && lane == 0) {
-                    publish(hh_ready);
-                    if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 6] = clock64();
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + col0;
+                __half *orow = p.hh_down + int64_t(row) * kPRank + col0;
+                bool ok = true;
+                for (int i = 0; i < p.T && ok; ++i) {
+                    ok = mbar_wait(&bar_acc_full[0], i & 1, abort_flag, 53);
+                    if (!ok) break;
+                    if (p.trace && int(blockIdx.x) == n_gate && threadIdx.x == 128) p.trace[i * 8 + 5] = clock64();
+                    tc_fence_after_sync();
+                    uint32_t acc0[32], acc1[32];
+                    tmem_ld_32x32(t_row, acc0);
+                    tmem_ld_32x32(t_row + 32, acc1);
+                    tmem_ld_wait();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_acc_empty[0]);
+                    if (row_ok) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int e = (8 * v + 2 * j) & 31;
+                                const uint32_t a0 = v < 4 ? acc0[e] : acc1[e];
+                                const uint32_t a1 = v < 4 ? acc0[e + 1] : acc1[e + 1];
+                                const __half2 h2 = __floats2half2_rn(float(int(a0)) * sc[8 * v + 2 * j],
+                                                                     float(int(a1)) * sc[8 * v + 2 * j + 1]);
+                                w[j] = *reinterpret_cast<const uint32_t *>(&h2);
+                            }
+                            *reinterpret_cast<uint4 *>(orow + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                    ok = warps_barrier(&bar_epi[0], i & 1, lane, abort_flag);
+                    if (ok && warp == 4 && lane == 0) {
+                        publish(hh_ready);
+                        if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 6] = clock64();
+                    }
                 }
             }
         }
@@ -559,19 +574,34 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
         if (rc) return rc;
     }
     // planes are strided by the FULL batch; the row extent is this launch's nb rows
-    rc = make_tmap_3d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_down + size_t(b0) * R, T, nb, R,
-                      uint64_t(R) * 2, uint64_t(Bfull) * R * 2, 128, 64, true);
+    // operand tiles come in with ONE instruction each: the maps walk the 128-byte K blocks of a
+    // row as a dimension of their own (stride 128 bytes) outside the rows, so a box holds the
+    // tile's K blocks one after the other, each in the 128-byte swizzle
+    {
+        const uint64_t dims[4] = {64, uint64_t(nb), 2, uint64_t(T)};
+        const uint64_t strides[3] = {uint64_t(R) * 2, 128, uint64_t(Bfull) * R * 2};
+        const uint32_t box[4] = {64, 128, 2, 1};
+        rc = make_tmap_nd(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_down + size_t(b0) * R, 4, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        rc = make_tmap_nd(&tm_hh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.hh_down, 3, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
+    rc = make_tmap_2d(&tm_dn, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, l->dn_hh_i8, R, H, H, kPRank, 128, true);
     if (rc) return rc;
-    rc = make_tmap_3d(&tm_hh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.hh_down, 1, nb, R, uint64_t(R) * 2,
-                      uint64_t(Bfull) * R * 2, 128, 64, true);
-    if (rc) return rc;
-    rc = make_tmap_2d(&tm_dn, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, l->dn_hh_i8, R, H, H, 64, 128, true);
-    if (rc) return rc;
-    rc = make_tmap_3d(&tm_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.h_out, T, nb, H, H, uint64_t(Bfull) * H, 128, 128, true);
-    if (rc) return rc;
-    rc = make_tmap_3d(&tm_h0, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<const int8_t *>(l->h_i8) + size_t(b0) * H, 1,
-                      nb, H, H, uint64_t(Bfull) * H, 128, 128, true);
-    if (rc) return rc;
+    // the workers' maps: boxes of 64 rows (a worker owns half a row tile) x all K blocks
+    {
+        const uint64_t dims[4] = {128, uint64_t(nb), uint64_t(p.nkb_h), uint64_t(T)};
+        const uint64_t strides[3] = {uint64_t(H), 128, uint64_t(Bfull) * H};
+        const uint32_t box[4] = {128, 64, uint32_t(p.nkb_h), 1};
+        rc = make_tmap_nd(&tm_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.h_out, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        const uint64_t dims0[4] = {128, uint64_t(nb), uint64_t(p.nkb_h), 1};
+        rc = make_tmap_nd(&tm_h0, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<const int8_t *>(l->h_i8) + size_t(b0) * H, 4,
+                          dims0, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
 
     const int grid = p.n_pairs * p.n_slices + p.n_tiles * kPWorkersPerTile;
     rc = (int)cudaMemsetAsync(flags, 0, sizeof(unsigned int) * (2 * p.n_tiles + 1), stream);

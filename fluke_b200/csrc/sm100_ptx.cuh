@@ -113,6 +113,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
 }
 
+// The same wait for warps that can afford a few tens of nanoseconds of wake-up delay: between
+// attempts the thread sleeps, so that the attempts of many waiting warps do not compete with the
+// tensor core's operand reads for the shared-memory pipe (a 128 x 128 x 32-byte MMA reads 8 KB in
+// 64 cycles: all of the pipe's 128 bytes per cycle).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                                  unsigned int site, unsigned int sleep_ns = 64) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            __nanosleep(sleep_ns);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycleLimit) {
+            report_timeout(site);
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), 2-D and 3-D tiles; loads complete on an mbarrier, stores are
 // tracked with bulk groups.
@@ -127,6 +150,15 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
         " [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
           "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m, uint64_t *bar,
+                                            int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
+          "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m, uint64_t *bar,

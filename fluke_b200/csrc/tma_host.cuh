@@ -84,4 +84,28 @@ inline int make_tmap_3d(CUtensorMap *m, CUtensorMapDataType dt, const void *base
                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
+// General form: `rank` dimensions (2..5), innermost first. dims/box in elements, strides in bytes
+// for dimensions 1..rank-1 (multiples of 16; they need not grow with the dimension, so a
+// dimension may walk the K blocks of a row while an outer one walks the rows). The innermost box
+// extent must span exactly 128 bytes under the 128-byte swizzle.
+inline int make_tmap_nd(CUtensorMap *m, CUtensorMapDataType dt, const void *base, int rank,
+                        const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box,
+                        CUtensorMapSwizzle swizzle) {
+    encode_tiled_fn fn = get_encode_tiled();
+    if (!fn) return (int)cudaErrorNotSupported;
+    if (rank < 2 || rank > 5) return (int)cudaErrorInvalidValue;
+    if (reinterpret_cast<uintptr_t>(base) & 15u) return (int)cudaErrorMisalignedAddress;
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], estr[5];
+    for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; estr[i] = 1; }
+    for (int i = 0; i + 1 < rank; ++i) {
+        if (strides_bytes[i] & 15u) return (int)cudaErrorMisalignedAddress;
+        st[i] = strides_bytes[i];
+    }
+    CUresult r = fn(m, dt, (cuuint32_t)rank, const_cast<void *>(base), d, st, b, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 }  // namespace fluke_sm100
