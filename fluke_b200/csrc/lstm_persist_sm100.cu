@@ -86,7 +86,8 @@ struct PersistSmem {
     static constexpr int kOffH = kPMaxHKB * kDnKB;
     static constexpr int kHKB = 64 * 128;                   // 64 rows of h x 128 B per K block
     // the MMA reads 128 rows per K block: one more block of slack behind the last one
-    static constexpr int kWorkerBytes = kOffH + (kPMaxHKB + 1) * kHKB;
+    static constexpr int kOffStage = kOffH + (kPMaxHKB + 1) * kHKB;  // outgoing hh_down rows: 2 blocks [64 x 128 B]
+    static constexpr int kWorkerBytes = kOffStage + 2 * 8192;
     static constexpr int kData = ((kGateBytes > kWorkerBytes ? kGateBytes : kWorkerBytes) + 15) / 16 * 16;
     static constexpr int kOffBars = kData;
     static constexpr int kNumBars = 12;
@@ -206,6 +207,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     const __grid_constant__ CUtensorMap tm_dn,   // dn_hh   [R,H]   int8
                     const __grid_constant__ CUtensorMap tm_h,    // h_out   [T,B,H] int8
                     const __grid_constant__ CUtensorMap tm_h0,   // h_0     [1,B,H] int8
+                    const __grid_constant__ CUtensorMap tm_hh_st,  // hh_down, boxes of a worker's 64 rows
                     const PersistDev p) {
     using L = PersistSmem<UNITS>;
     extern __shared__ uint8_t smem_raw[];
@@ -476,8 +478,6 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             const int q = warp & 3;
             if (q < 2) {
                 const int chalf = (warp - 2) >> 2;
-                const int row = m0 + q * 32 + lane;
-                const bool row_ok = row < p.B;
                 const int col0 = chalf * 64;
                 float sc[64];
 #pragma unroll
@@ -488,7 +488,12 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     sc[4 * v + 2] = (1.0f / 127.0f) * s4.z; sc[4 * v + 3] = (1.0f / 127.0f) * s4.w;
                 }
                 const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + col0;
-                __half *orow = p.hh_down + int64_t(row) * kPRank + col0;
+                // The rows leave through shared memory and ONE bulk tensor store: a thread owns a
+                // row, so direct stores would be 32 separate 16-byte pieces per instruction. The
+                // staging tile is two blocks (column halves) of 64 rows x 128 bytes in the 128-byte
+                // swizzle, which also makes the 16-byte writes of a warp conflict-free.
+                const int srow = q * 32 + lane;
+                uint8_t *stage_row = smem + L::kOffStage + chalf * 8192 + srow * 128;
                 bool ok = true;
                 for (int i = 0; i < p.T && ok; ++i) {
                     ok = mbar_wait(&bar_acc_full[0], i & 1, abort_flag, 53);
@@ -502,24 +507,27 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bar_acc_empty[0]);
-                    if (row_ok) {
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            uint32_t w[4];
+                    for (int v = 0; v < 8; ++v) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int e = (8 * v + 2 * j) & 31;
-                                const uint32_t a0 = v < 4 ? acc0[e] : acc1[e];
-                                const uint32_t a1 = v < 4 ? acc0[e + 1] : acc1[e + 1];
-                                const __half2 h2 = __floats2half2_rn(float(int(a0)) * sc[8 * v + 2 * j],
-                                                                     float(int(a1)) * sc[8 * v + 2 * j + 1]);
-                                w[j] = *reinterpret_cast<const uint32_t *>(&h2);
-                            }
-                            *reinterpret_cast<uint4 *>(orow + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int j = 0; j < 4; ++j) {
+                            const int e = (8 * v + 2 * j) & 31;
+                            const uint32_t a0 = v < 4 ? acc0[e] : acc1[e];
+                            const uint32_t a1 = v < 4 ? acc0[e + 1] : acc1[e + 1];
+                            const __half2 h2 = __floats2half2_rn(float(int(a0)) * sc[8 * v + 2 * j],
+                                                                 float(int(a1)) * sc[8 * v + 2 * j + 1]);
+                            w[j] = *reinterpret_cast<const uint32_t *>(&h2);
                         }
+                        *reinterpret_cast<uint4 *>(stage_row + ((v ^ (srow & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
+                    fence_proxy_async_smem();
                     ok = warps_barrier(&bar_epi[0], i & 1, lane, abort_flag);
                     if (ok && warp == 4 && lane == 0) {
+                        // rows past the end of the batch are clipped by the store
+                        tma_store_3d(&tm_hh_st, smem + L::kOffStage, 0, m0, 0);
+                        tma_store_commit();
+                        tma_store_wait_all<0>();
                         publish(hh_ready);
                         if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 6] = clock64();
                     }
@@ -566,7 +574,7 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
     p.flags = flags;
     p.trace = g_persist_trace;
 
-    CUtensorMap tm_w[4], tm_x, tm_hh, tm_dn, tm_h, tm_h0;
+    CUtensorMap tm_w[4], tm_x, tm_hh, tm_dn, tm_h, tm_h0, tm_hh_st;
     int rc;
     for (int g = 0; g < 4; ++g) {
         const __half *w = static_cast<const __half *>(l->w_up_f16) + size_t(g) * H * 2 * R;
@@ -585,6 +593,10 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
         rc = make_tmap_nd(&tm_hh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.hh_down, 3, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        const uint32_t box_st[3] = {64, 64, 2};  // a worker's half of a row tile
+        rc = make_tmap_nd(&tm_hh_st, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.hh_down, 3, dims, strides, box_st,
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
@@ -606,7 +618,7 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
     const int grid = p.n_pairs * p.n_slices + p.n_tiles * kPWorkersPerTile;
     rc = (int)cudaMemsetAsync(flags, 0, sizeof(unsigned int) * (2 * p.n_tiles + 1), stream);
     if (rc) return rc;
-    void *args[] = {&tm_w[0], &tm_w[1], &tm_w[2], &tm_w[3], &tm_x, &tm_hh, &tm_dn, &tm_h, &tm_h0, &p};
+    void *args[] = {&tm_w[0], &tm_w[1], &tm_w[2], &tm_w[3], &tm_x, &tm_hh, &tm_dn, &tm_h, &tm_h0, &tm_hh_st, &p};
     return (int)cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kernel), dim3(grid), dim3(kPThreads),
                                             args, PersistSmem<UNITS>::kDynamic, stream);
 }
