@@ -89,7 +89,8 @@ def _run_oracle_layer(layer, x, xs, reverse, c0=None, h0=None):
                            n(layer.dn_hh_scale), n(layer.w_up), n(layer.bias), c0, h0, reverse)
 
 
-@pytest.mark.parametrize("T,B,reverse", [(12, 200, False), (12, 200, True), (40, 128, False), (3, 1, True)])
+@pytest.mark.parametrize("T,B,reverse", [(12, 200, False), (12, 200, True), (40, 128, False), (3, 1, True),
+                                         (6, 330, True), (5, 60, False)])
 def test_layer_vs_oracle(T, B, reverse, lstm_mode):
     H, R = 768, 128
     layer, x, xs = _layer_case(T, B, H, R, 42 + T, reverse)
@@ -149,9 +150,10 @@ def test_stack_alternating_directions_and_batch_shards(lstm_mode):
 
 def test_persistent_and_per_step_layers_agree(flib):
     """Same layer through all three drivers: the only difference is the accumulation order of the two
-    K halves, so codes differ by at most one, rarely. Also a hidden size of 1024 (64 units per CTA)
-    and a batch that is not a multiple of the 128-row tile."""
-    for (T, B, H) in [(16, 300, 768), (6, 130, 1024), (5, 1024, 768)]:
+    K halves, so codes differ by at most one, rarely. Also other hidden sizes (1024, 384 with an odd
+    number of 128-byte K blocks, 512), batches that are not a multiple of the 128-row tile and one
+    with more row tiles than one single-launch kernel holds."""
+    for (T, B, H) in [(16, 300, 768), (6, 130, 1024), (5, 1024, 768), (4, 140, 384), (4, 70, 512), (3, 1100, 768)]:
         layer, x, xs = _layer_case(T, B, H, 128, 11 + B, False)
         outs = []
         for mode in (1, 2, 0):
