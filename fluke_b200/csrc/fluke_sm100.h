@@ -129,6 +129,12 @@ int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, void *strea
  * (R = 128, H a multiple of 128 up to 1024); 2: the L2-exchange form only; 0: always two launches
  * per timestep. */
 void fluke_sm100_set_lstm_persistent(int mode);
+/* Configuration of the L2-exchange form. Narrow: 24 or 32 hidden units per gate CTA, two workers
+ * per row tile (8 row tiles per launch on 148 SMs at H = 768). Wide: 48 units per gate CTA, one
+ * worker per row tile, for H = 384 or 768: 16 row tiles per launch, a step about 15 % longer.
+ * -1 (default): wide when the layer has more row tiles than a narrow launch holds; 0: never;
+ * 1: whenever the shape allows it. */
+void fluke_sm100_set_lstm_wide(int mode);
 /* Which form the last whole-layer call used: 1 cluster exchange, 2 L2 exchange, 0 per step. */
 int fluke_sm100_lstm_last_form(void);
 /* Row tiles (clusters) of the cluster form that run at once for hidden size H; 0 = unavailable. */

@@ -46,11 +46,8 @@ namespace fluke_sm100 {
 namespace {
 
 constexpr int kPThreads = 320;          // warp 0 producer, warp 1 MMA, warps 2-5 / 6-9 epilogue
-constexpr int kPWorkersPerTile = 2;     // each projects 64 of the tile's 128 rows
 constexpr int kPRank = 128;             // factor rank the kernel is built for
 constexpr int kPMaxHKB = 8;             // hidden K blocks of 128 bytes: H <= 1024
-constexpr int kPTmemCols = 256;
-constexpr int kPAccStride = 128;        // TMEM columns between the two tiles' accumulators
 
 struct PersistDev {
     int T, B, H;               // B: chunks handled by this launch
@@ -71,8 +68,16 @@ struct PersistDev {
 // record clock64() at the hand-over points of every step.
 static long long *g_persist_trace = nullptr;
 
-template <int UNITS>
+// UNITS: hidden units per gate CTA. WPT: worker CTAs per row tile, 2 (each takes 64 of the
+// tile's rows) or 1 (the whole tile; for the wide configuration, where the SMs go to twice as
+// many row tiles instead).
+template <int UNITS, int WPT>
 struct PersistSmem {
+    static_assert(WPT == 1 || WPT == 2, "one or two workers per row tile");
+    // tensor memory: one accumulator of 4*UNITS columns per tile of the pair (gate role); the
+    // worker's accumulator has kPRank columns
+    static constexpr int kAccStride = (4 * UNITS <= 128) ? 128 : 256;
+    static constexpr int kTmemCols = 2 * kAccStride;
     // gate role
     static constexpr int kWKB = 4 * UNITS * 128;           // one K block of the four gate slices
     static constexpr int kOffW = 0;                         // 4 K blocks
@@ -81,13 +86,19 @@ struct PersistSmem {
     static constexpr int kOffBias = kOffX + 2 * 32768;      // 4 x UNITS floats
     static constexpr int kGateBytes = kOffBias + 4 * UNITS * 4;
     // worker role
+    static constexpr int kWorkerRows = 128 / WPT;           // rows of the tile a worker projects
+    static constexpr int kMaxHKB = (WPT == 2) ? kPMaxHKB : 6;  // hidden K blocks the layout holds
     static constexpr int kDnKB = kPRank * 128;              // R projection rows x 128 B
     static constexpr int kOffDn = 0;
     static constexpr int kOffH = kPMaxHKB * kDnKB;
-    static constexpr int kHKB = 64 * 128;                   // 64 rows of h x 128 B per K block
-    // the MMA reads 128 rows per K block: one more block of slack behind the last one
-    static constexpr int kOffStage = kOffH + (kPMaxHKB + 1) * kHKB;  // outgoing hh_down rows: 2 blocks [64 x 128 B]
-    static constexpr int kWorkerBytes = kOffStage + 2 * 8192;
+    static constexpr int kHKB = kWorkerRows * 128;          // the worker's rows of h x 128 B per K block
+    static constexpr int kStageBytes = 2 * kWorkerRows * 128;  // outgoing hh_down rows: 2 column halves
+    // WPT == 2: the MMA reads 128 rows per K block, 64 of them behind the worker's own: one block
+    // of slack after the last, then the staging tile. WPT == 1: the staging tile sits in the part
+    // of the weight area that at most 6 K blocks leave free.
+    static constexpr int kOffStage = (WPT == 2) ? kOffH + (kPMaxHKB + 1) * kHKB : kMaxHKB * kDnKB;
+    static constexpr int kWorkerBytes = (WPT == 2) ? kOffStage + kStageBytes : kOffH + kMaxHKB * kHKB;
+    static_assert(WPT == 2 || kOffStage + kStageBytes <= kOffH, "staging tile overlaps the h tile");
     static constexpr int kData = ((kGateBytes > kWorkerBytes ? kGateBytes : kWorkerBytes) + 15) / 16 * 16;
     static constexpr int kOffBars = kData;
     static constexpr int kNumBars = 12;
@@ -198,7 +209,7 @@ __device__ __forceinline__ uint32_t lstm_cell_pair(uint32_t gi0, uint32_t gi1, u
     return (uint32_t(__float2int_rz(hx)) & 0xFFu) | ((uint32_t(__float2int_rz(hy)) & 0xFFu) << 8);
 }
 
-template <int UNITS>
+template <int UNITS, int WPT>
 __global__ void __launch_bounds__(kPThreads, 1)
 lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
                     const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_w3,
@@ -209,7 +220,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     const __grid_constant__ CUtensorMap tm_h0,   // h_0     [1,B,H] int8
                     const __grid_constant__ CUtensorMap tm_hh_st,  // hh_down, boxes of a worker's 64 rows
                     const PersistDev p) {
-    using L = PersistSmem<UNITS>;
+    using L = PersistSmem<UNITS, WPT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -233,16 +244,16 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
         mbar_init(bar_once, 1);
         for (int g = 0; g < 2; ++g) {
             mbar_init(&bar_acc_full[g], 1);
-            mbar_init(&bar_acc_empty[g], 4);
+            mbar_init(&bar_acc_empty[g], (is_gate || WPT == 2) ? 4 : 8);
             mbar_init(&bar_x[g], 1);
             mbar_init(&bar_ahh[g], 1);
-            mbar_init(&bar_epi[g], 4);
+            mbar_init(&bar_epi[g], (is_gate || WPT == 2) ? 4 : 8);
         }
         mbar_init(bar_h, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, kPTmemCols);
+    if (warp == 1) tmem_alloc(tmem_slot, L::kTmemCols);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -278,7 +289,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     }
                     for (int g = 0; g < n_local && ok; ++g) {
                         const int tile = 2 * pair + g;
-                        ok = wait_counter(p.flags + p.n_tiles + tile, (unsigned)(kPWorkersPerTile * (i + 1)),
+                        ok = wait_counter(p.flags + p.n_tiles + tile, (unsigned)(WPT * (i + 1)),
                                           g_abort, abort_flag, 33);
                         if (!ok) break;
                         if (p.trace && blockIdx.x == 0 && g == 0) p.trace[i * 8 + 0] = clock64();
@@ -308,7 +319,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                             const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffW + (2 + kb) * L::kWKB));
 #pragma unroll
                             for (int k = 0; k < 4; ++k)
-                                tc_mma<kKindF16>(tmem_base + g * kPAccStride, ad + uint64_t(2 * k),
+                                tc_mma<kKindF16>(tmem_base + g * L::kAccStride, ad + uint64_t(2 * k),
                                                  bd + uint64_t(2 * k), kIdesc, (kb | k) != 0 ? 1u : 0u);
                         }
                     }
@@ -326,7 +337,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                             const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffW + kb * L::kWKB));
 #pragma unroll
                             for (int k = 0; k < 4; ++k)
-                                tc_mma<kKindF16>(tmem_base + g * kPAccStride, ad + uint64_t(2 * k),
+                                tc_mma<kKindF16>(tmem_base + g * L::kAccStride, ad + uint64_t(2 * k),
                                                  bd + uint64_t(2 * k), kIdesc, 1u);
                         }
                         tc_commit(&bar_acc_full[g]);
@@ -359,7 +370,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
 #pragma unroll
                     for (int v = 0; v < UNITS / 2; ++v) c2[v] = make_float2(0.f, 0.f);
                 }
-                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + g * kPAccStride;
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + g * L::kAccStride;
                 unsigned int *h_ready = p.flags + tile;
                 bool ok = true;
                 for (int i = 0; i < p.T && ok; ++i) {
@@ -418,8 +429,8 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             }
         }
     } else {
-        const int tile = (blockIdx.x - n_gate) / kPWorkersPerTile;
-        const int m0 = tile * 128 + ((blockIdx.x - n_gate) % kPWorkersPerTile) * 64;  // first row of this worker
+        const int tile = (blockIdx.x - n_gate) / WPT;
+        const int m0 = tile * 128 + ((blockIdx.x - n_gate) % WPT) * L::kWorkerRows;  // first row of this worker
         unsigned int *h_ready = p.flags + tile;
         unsigned int *hh_ready = p.flags + p.n_tiles + tile;
         if (warp == 0) {
@@ -459,7 +470,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     if (!ok) break;
                     tc_fence_after_sync();
                     for (int kb = 0; kb < p.nkb_h; ++kb) {
-                        // rows 64-127 of the operand overlap the next K block (or the slack)
+                        // WPT == 2: rows 64-127 of the operand overlap the next K block (or the slack)
                         const uint64_t ad = make_smem_desc_sw128(smem_u32(smem + L::kOffH + kb * L::kHKB));
                         const uint64_t bd = make_smem_desc_sw128(smem_u32(smem + L::kOffDn + kb * L::kDnKB));
 #pragma unroll
@@ -473,10 +484,11 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             __syncwarp();
         } else {
             // ------------------------------ worker: epilogue ----------------------------
-            // The valid accumulator rows are TMEM lanes 0-63: only the warps of lane quadrants 0
-            // and 1 take part (two per quadrant, 64 projection columns each).
+            // The valid accumulator rows are TMEM lanes 0 .. kWorkerRows-1: with two workers per tile
+            // only the warps of lane quadrants 0 and 1 take part (two per quadrant, 64 projection
+            // columns each).
             const int q = warp & 3;
-            if (q < 2) {
+            if (q * 32 < L::kWorkerRows) {
                 const int chalf = (warp - 2) >> 2;
                 const int col0 = chalf * 64;
                 float sc[64];
@@ -493,7 +505,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                 // staging tile is two blocks (column halves) of 64 rows x 128 bytes in the 128-byte
                 // swizzle, which also makes the 16-byte writes of a warp conflict-free.
                 const int srow = q * 32 + lane;
-                uint8_t *stage_row = smem + L::kOffStage + chalf * 8192 + srow * 128;
+                uint8_t *stage_row = smem + L::kOffStage + chalf * (L::kStageBytes / 2) + srow * 128;
                 bool ok = true;
                 for (int i = 0; i < p.T && ok; ++i) {
                     ok = mbar_wait(&bar_acc_full[0], i & 1, abort_flag, 53);
@@ -540,25 +552,25 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, kPTmemCols);
+        tmem_dealloc(tmem_base, L::kTmemCols);
     }
 }
 
 // ---- host side ---------------------------------------------------------------------------------
 
-template <int UNITS>
+template <int UNITS, int WPT>
 int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *hh_down,
                    unsigned int *flags, int b0, int nb, cudaStream_t stream) {
     // one launch handles chunks [b0, b0+nb); all pointers below are offset to that range
     const int T = l->T, H = l->H, R = l->R, Bfull = l->B;
-    auto kernel = lstm_persist_kernel<UNITS>;
+    auto kernel = lstm_persist_kernel<UNITS, WPT>;
     static bool done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             PersistSmem<UNITS>::kDynamic);
+                                             PersistSmem<UNITS, WPT>::kDynamic);
         if (e != cudaSuccess) return (int)e;
         done[dev] = true;
     }
@@ -595,18 +607,18 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
         rc = make_tmap_nd(&tm_hh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.hh_down, 3, dims, strides, box,
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
-        const uint32_t box_st[3] = {64, 64, 2};  // a worker's half of a row tile
+        const uint32_t box_st[3] = {64, 128 / WPT, 2};  // a worker's rows of a row tile
         rc = make_tmap_nd(&tm_hh_st, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.hh_down, 3, dims, strides, box_st,
                           CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
     rc = make_tmap_2d(&tm_dn, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, l->dn_hh_i8, R, H, H, kPRank, 128, true);
     if (rc) return rc;
-    // the workers' maps: boxes of 64 rows (a worker owns half a row tile) x all K blocks
+    // the workers' maps: boxes of a worker's rows (half a row tile, or all of it) x all K blocks
     {
         const uint64_t dims[4] = {128, uint64_t(nb), uint64_t(p.nkb_h), uint64_t(T)};
         const uint64_t strides[3] = {uint64_t(H), 128, uint64_t(Bfull) * H};
-        const uint32_t box[4] = {128, 64, uint32_t(p.nkb_h), 1};
+        const uint32_t box[4] = {128, 128 / WPT, uint32_t(p.nkb_h), 1};
         rc = make_tmap_nd(&tm_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.h_out, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
         const uint64_t dims0[4] = {128, uint64_t(nb), uint64_t(p.nkb_h), 1};
@@ -615,31 +627,31 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
         if (rc) return rc;
     }
 
-    const int grid = p.n_pairs * p.n_slices + p.n_tiles * kPWorkersPerTile;
+    const int grid = p.n_pairs * p.n_slices + p.n_tiles * WPT;
     rc = (int)cudaMemsetAsync(flags, 0, sizeof(unsigned int) * (2 * p.n_tiles + 1), stream);
     if (rc) return rc;
     void *args[] = {&tm_w[0], &tm_w[1], &tm_w[2], &tm_w[3], &tm_x, &tm_hh, &tm_dn, &tm_h, &tm_h0, &tm_hh_st, &p};
     return (int)cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kernel), dim3(grid), dim3(kPThreads),
-                                            args, PersistSmem<UNITS>::kDynamic, stream);
+                                            args, PersistSmem<UNITS, WPT>::kDynamic, stream);
 }
 
 // Largest number of 128-row tiles whose CTAs are all co-resident, or 0 when the device cannot
 // run the kernel cooperatively.
-template <int UNITS>
+template <int UNITS, int WPT>
 int persist_max_tiles(int H) {
     int dev = 0, sms = 0, per_sm = 0, coop = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
-    auto kernel = lstm_persist_kernel<UNITS>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistSmem<UNITS>::kDynamic) != cudaSuccess)
+    auto kernel = lstm_persist_kernel<UNITS, WPT>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistSmem<UNITS, WPT>::kDynamic) != cudaSuccess)
         return 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPThreads, PersistSmem<UNITS>::kDynamic) != cudaSuccess)
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPThreads, PersistSmem<UNITS, WPT>::kDynamic) != cudaSuccess)
         return 0;
     if (!coop || per_sm < 1) return 0;
     const int slots = sms * per_sm, slices = H / UNITS;
     int tiles = 0;
-    while (((tiles + 2) / 2) * slices + (tiles + 1) * kPWorkersPerTile <= slots) ++tiles;
+    while (((tiles + 2) / 2) * slices + (tiles + 1) * WPT <= slots) ++tiles;
     return tiles;
 }
 
@@ -650,6 +662,12 @@ extern "C" void fluke_sm100_lstm_set_trace(void *device_buffer) {
     fluke_sm100::g_persist_trace = static_cast<long long *>(device_buffer);
 }
 
+// -1: the wide configuration (48 units per gate CTA, one worker per row tile: twice the row tiles
+// per launch) is used when the layer has more row tiles than one launch of the narrow one holds;
+// 0: never; 1: whenever the shape allows it.
+static int g_lstm_wide = -1;
+extern "C" void fluke_sm100_set_lstm_wide(int mode) { g_lstm_wide = mode < 0 ? -1 : (mode > 0 ? 1 : 0); }
+
 // Runs the recurrence of one layer (x_down already computed) with persistent launches. Returns
 // -2 when the shape is not covered (the caller then uses the per-step kernels).
 extern "C" int fluke_sm100_lstm_layer_persistent(const void *layer, const void *x_down, void *hh_down,
@@ -658,18 +676,27 @@ extern "C" int fluke_sm100_lstm_layer_persistent(const void *layer, const void *
     const fluke_flstm_layer_t *l = static_cast<const fluke_flstm_layer_t *>(layer);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (l->R != kPRank || l->H % 128 || l->H > 128 * kPMaxHKB) return -2;
-    // hidden units per gate CTA: 24 where H allows it (H = 768 -> 32 slices), else 32
+    const __half *xd = static_cast<const __half *>(x_down);
+    __half *hd = static_cast<__half *>(hh_down);
+    unsigned int *fl = static_cast<unsigned int *>(flags);
+    // narrow configuration: hidden units per gate CTA 24 where H allows it (H = 768 -> 32 slices),
+    // else 32; two workers per row tile
     const int units = (l->H % 24 == 0) ? 24 : 32;
-    const int max_tiles = units == 24 ? persist_max_tiles<24>(l->H) : persist_max_tiles<32>(l->H);
+    const int narrow_tiles = units == 24 ? persist_max_tiles<24, 2>(l->H) : persist_max_tiles<32, 2>(l->H);
+    // wide configuration: 48 units per gate CTA, one worker per row tile
+    const bool wide_ok = l->H % 48 == 0 && l->H <= 128 * PersistSmem<48, 1>::kMaxHKB;
+    const int wide_tiles = wide_ok ? persist_max_tiles<48, 1>(l->H) : 0;
+    const int tiles = (l->B + 127) / 128;
+    const bool wide = wide_tiles > 0 && (g_lstm_wide == 1 || narrow_tiles < 1 ||
+                                         (g_lstm_wide == -1 && tiles > narrow_tiles && wide_tiles > narrow_tiles));
+    const int max_tiles = wide ? wide_tiles : narrow_tiles;
     if (max_tiles < 1) return -2;
     const int tiles_per_launch = max_tiles > 64 ? 64 : max_tiles;  // the counter block holds 2*64+1 words
     for (int b0 = 0; b0 < l->B; b0 += tiles_per_launch * 128) {
         const int nb = l->B - b0 < tiles_per_launch * 128 ? l->B - b0 : tiles_per_launch * 128;
-        const int rc = units == 24
-                           ? persist_launch<24>(l, static_cast<const __half *>(x_down), static_cast<__half *>(hh_down),
-                                                static_cast<unsigned int *>(flags), b0, nb, stream)
-                           : persist_launch<32>(l, static_cast<const __half *>(x_down), static_cast<__half *>(hh_down),
-                                                static_cast<unsigned int *>(flags), b0, nb, stream);
+        const int rc = wide ? persist_launch<48, 1>(l, xd, hd, fl, b0, nb, stream)
+                            : (units == 24 ? persist_launch<24, 2>(l, xd, hd, fl, b0, nb, stream)
+                                           : persist_launch<32, 2>(l, xd, hd, fl, b0, nb, stream));
         if (rc) return rc;
     }
     return 0;

@@ -80,6 +80,7 @@ SIGNATURES = {
     "fluke_sm100_read_status": (I, [ctypes.POINTER(ctypes.c_uint), I]),
     "fluke_sm100_mma_peak": (I, [I, I, I, P, I, P]),
     "fluke_sm100_lstm_last_form": (I, []),
+    "fluke_sm100_set_lstm_wide": (None, [I]),
     "fluke_sm100_lstm_cluster_capacity": (I, [I]),
 }
 for _n, _a in VOID_SIGNATURES.items():

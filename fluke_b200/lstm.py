@@ -67,67 +67,113 @@ def run_stack(layers, x_i8, x_scale, state=None, workspace=None, buffers=None):
 
 
 class StackPipeline:
-    """Host-to-host streaming of whole stack passes: while pass k runs the layers on the compute
-    stream, the input of pass k+1 is copied in and the output of pass k-1 is copied out on two
-    copy streams (the two PCIe directions are independent), so in steady state a pass costs
-    max(compute, copy-in, copy-out) instead of their sum.
+    """Host-to-host streaming of whole stack passes: while one group of passes runs the layers on
+    the compute stream, the inputs of the next are copied in and the outputs of the one before are
+    copied out on two copy streams (the two PCIe directions are independent), so in steady state a
+    pass costs max(compute, copy-in, copy-out) instead of their sum.
+
+    `passes_per_launch` = P > 1 puts P consecutive passes side by side in one batch of P*B chunks
+    and runs each layer once over it (chunks are independent, so the results are those of the
+    separate passes). The recurrence is a latency-bound chain, and a layer call over twice the
+    chunks costs far less than two calls (the wide single-launch configuration holds 16 row tiles).
+    The results of a pass are then complete when its group has run: after the P-th `submit` of
+    the group, or after `drain()`, which also runs a group that is only partly filled.
 
     Device memory: two input sets, the two ping-pong layer buffers and two output buffers of
-    [T,B,H] int8. Inputs and outputs are pinned host tensors; `submit` only enqueues work."""
+    [T,P*B,H] int8. Inputs and outputs are pinned host tensors; `submit` only enqueues work."""
 
-    def __init__(self, layers, T, B, device):
+    def __init__(self, layers, T, B, device, passes_per_launch=1):
         self.layers = layers
         h = layers[0].hidden
+        P = int(passes_per_launch)
+        assert P >= 1
+        self.P = P
         self.shape = (T, B, h)
         dev = torch.device(device)
         self.device = dev
-        mk = lambda: torch.empty(T, B, h, dtype=torch.int8, device=dev)
+        mk = lambda: torch.zeros(T, P * B, h, dtype=torch.int8, device=dev)
         self.x = [mk(), mk()]
-        self.xs = [torch.empty(T * B, dtype=torch.float32, device=dev) for _ in range(2)]
+        self.xs = [torch.zeros(T * P * B, dtype=torch.float32, device=dev) for _ in range(2)]
         self.bufs = [mk(), mk()]
         self.out = [mk(), mk()]
-        self.state = [[(torch.zeros(B, h, dtype=torch.float32, device=dev),
-                        torch.zeros(B, h, dtype=torch.int8, device=dev)) for _ in layers] for _ in range(2)]
-        need = ops._L().fluke_factored_lstm_layer_workspace(T, B, h, layers[0].rank)
+        self.state = [[(torch.zeros(P * B, h, dtype=torch.float32, device=dev),
+                        torch.zeros(P * B, h, dtype=torch.int8, device=dev)) for _ in layers] for _ in range(2)]
+        need = ops._L().fluke_factored_lstm_layer_workspace(T, P * B, h, layers[0].rank)
         self.ws = torch.empty(need, dtype=torch.uint8, device=dev)
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
-        self.ev_in = [torch.cuda.Event() for _ in range(2)]     # input set k%2 copied in
-        self.ev_run = [torch.cuda.Event() for _ in range(2)]    # pass that used slot k%2 finished computing
-        self.ev_out = [torch.cuda.Event() for _ in range(2)]    # output buffer k%2 copied out
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]     # inputs of the group in slot g%2 copied in
+        self.ev_run = [torch.cuda.Event() for _ in range(2)]    # group that used slot g%2 finished computing
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]    # output buffer g%2 copied out
         self.k = 0
+        self.pending = []   # host output tensors of the group being filled
+
+    def _block(self, t, j):
+        """Pass j's columns of a [T, P*B, ...] device tensor."""
+        T, B, _ = self.shape
+        return t.view(T, self.P, B, *t.shape[2:])[:, j]
 
     def submit(self, x_host, xs_host, out_host, zero_state=True):
         """Enqueue one pass: x_host int8 [T,B,H] and xs_host f32 [T*B] (pinned) in, the last layer's
-        int8 output into out_host (pinned). Returns the event that marks out_host complete."""
-        k, slot = self.k, self.k % 2
+        int8 output into out_host (pinned). Every pass starts from a zero state unless
+        zero_state=False (then the group continues from the state its slot last held). Returns the
+        event that marks the outputs of the pass's group complete, or None while the group is
+        still being filled."""
+        T, B, _ = self.shape
+        k, g = self.k, self.k // self.P
+        j, slot = k % self.P, g % 2
         self.k += 1
         cur = torch.cuda.current_stream(self.device)
-        # copy-in: the slot's previous pass (k-2) must have finished reading it
-        self.s_in.wait_stream(cur)
-        if k >= 2:
-            self.s_in.wait_event(self.ev_run[slot])
+        # copy-in: the slot's previous group (g-2) must have finished reading it
+        if j == 0:
+            self.s_in.wait_stream(cur)
+            if g >= 2:
+                self.s_in.wait_event(self.ev_run[slot])
         with torch.cuda.stream(self.s_in):
-            self.x[slot].copy_(x_host, non_blocking=True)
-            self.xs[slot].copy_(xs_host, non_blocking=True)
+            if self.P == 1:
+                self.x[slot].copy_(x_host, non_blocking=True)
+                self.xs[slot].copy_(xs_host, non_blocking=True)
+            else:
+                self._block(self.x[slot], j).copy_(x_host, non_blocking=True)
+                self.xs[slot].view(T, self.P, B)[:, j].copy_(xs_host.view(T, B), non_blocking=True)
             self.ev_in[slot].record()
-        # compute: after its input is in, and after the copy-out that last read this output buffer
+        self.pending.append(out_host)
+        if j == self.P - 1:
+            return self._launch(slot, g, zero_state)
+        self._zero_state = zero_state
+        return None
+
+    def _launch(self, slot, g, zero_state):
+        # compute: after the group's inputs are in, and after the copy-out that last read this output buffer
+        T, B, H = self.shape
+        filled = len(self.pending)
+        Bf = filled * B
         self.s_run.wait_event(self.ev_in[slot])
-        if k >= 2:
+        if g >= 2:
             self.s_run.wait_event(self.ev_out[slot])
         lib = ops._L()
         prev_stream = lib.fluke_get_stream()
         lib.fluke_set_stream(self.s_run.cuda_stream)
+        # a partly filled group runs over its own chunks only: the buffers are used as flat
+        # memory holding [T, filled*B, H]
+        flat = lambda t: t.view(-1)[:T * Bf * H].view(T, Bf, H)
         try:
             with torch.cuda.stream(self.s_run):
+                state = [(c[:Bf], hs[:Bf]) for c, hs in self.state[slot]]
                 if zero_state:
-                    for c, hs in self.state[slot]:
+                    for c, hs in state:
                         c.zero_()
                         hs.zero_()
-                cur_x, cur_s = self.x[slot], self.xs[slot]
+                if filled == self.P:
+                    cur_x, cur_s = self.x[slot], self.xs[slot]
+                else:
+                    cur_x = flat(self.bufs[1])   # free until the second layer writes it
+                    cur_x.view(T, filled, B, H).copy_(self.x[slot].view(T, self.P, B, H)[:, :filled])
+                    cur_s = self.xs[slot].view(T, self.P, B)[:, :filled].reshape(T * Bf)
+                out = flat(self.out[slot])
                 n = len(self.layers)
                 for i, layer in enumerate(self.layers):
-                    c, hs = self.state[slot][i]
-                    dst = self.out[slot] if i == n - 1 else self.bufs[i % 2]
+                    c, hs = state[i]
+                    dst = out if i == n - 1 else flat(self.bufs[i % 2])
                     ops.factored_lstm_layer_i8(cur_x, cur_s, layer.dn_ih, layer.dn_ih_scale, layer.dn_hh,
                                                layer.dn_hh_scale, layer.w_up, layer.bias, c, hs,
                                                reverse=layer.reverse, h_out=dst, workspace=self.ws)
@@ -138,12 +184,19 @@ class StackPipeline:
         # copy-out
         self.s_out.wait_event(self.ev_run[slot])
         with torch.cuda.stream(self.s_out):
-            out_host.copy_(self.out[slot], non_blocking=True)
+            for j, out_host in enumerate(self.pending):
+                out_host.copy_(out if filled == 1 else out.view(T, filled, B, H)[:, j], non_blocking=True)
             self.ev_out[slot].record()
+        self.pending = []
         return self.ev_out[slot]
 
     def drain(self):
-        """Make the current stream wait for everything submitted so far."""
+        """Run a group that is only partly filled (over its own chunks only), then make the current
+        stream wait for everything submitted so far."""
+        if self.pending:
+            g = (self.k - 1) // self.P
+            self.k = (g + 1) * self.P   # the next pass starts a new group
+            self._launch(g % 2, g, getattr(self, "_zero_state", True))
         cur = torch.cuda.current_stream(self.device)
         cur.wait_stream(self.s_in)
         cur.wait_stream(self.s_run)

@@ -215,22 +215,49 @@ def test_layer_config_size_properties(lstm_mode):
         assert torch.equal(h3, fwd[0])
 
 
-def test_streaming_pipeline_equals_pass_by_pass():
-    """Four passes with different inputs through the three-stream driver (copy-in, layers,
-    copy-out overlapped across passes) give the bytes of run_stack on each input alone."""
+@pytest.mark.parametrize("passes_per_launch", [1, 2])
+def test_streaming_pipeline_equals_pass_by_pass(passes_per_launch):
+    """Five passes with different inputs through the three-stream driver (copy-in, layers,
+    copy-out overlapped across groups of passes) give the bytes of run_stack on each input alone;
+    with two passes per launch the fifth is a group of its own that `drain` runs."""
     T, B, H, R, NL = 6, 200, 768, 128, 3
     g = torch.Generator().manual_seed(77)
     layers = [FactoredLstmLayer.random(H, R, bool(i % 2), g, DEV) for i in range(NL)]
-    pipe = StackPipeline(layers, T, B, DEV)
+    pipe = StackPipeline(layers, T, B, DEV, passes_per_launch=passes_per_launch)
     ins, outs = [], []
-    for k in range(4):
+    for k in range(5):
         x, xs = prep.quantize_int8_rows(torch.randn(T * B, H, generator=g))
         ins.append((x.view(T, B, H).contiguous().pin_memory(), xs.contiguous().pin_memory()))
         outs.append(torch.empty(T, B, H, dtype=torch.int8).pin_memory())
-    for k in range(4):
+    for k in range(5):
         pipe.submit(ins[k][0], ins[k][1], outs[k])
     pipe.drain()
     torch.cuda.synchronize()
-    for k in range(4):
+    for k in range(5):
         ref, _ = run_stack(layers, ins[k][0].to(DEV), ins[k][1].to(DEV))
         assert torch.equal(outs[k], ref.cpu())
+
+
+def test_wide_l2_configuration_matches_the_narrow_one(flib):
+    """The L2-exchange form with 48 units per gate CTA and one worker per row tile (chosen by itself
+    when a layer has more row tiles than a narrow launch holds) computes every element in the same
+    order as the narrow configuration: identical bytes. Shapes: ragged tiles, H = 384, and a batch
+    of 2100 chunks (17 row tiles: one full wide launch and a second one)."""
+    for (T, B, H) in [(6, 300, 768), (5, 130, 384), (3, 2100, 768), (4, 1, 768)]:
+        layer, x, xs = _layer_case(T, B, H, 128, 3 + B, False)
+        res = []
+        for wide in (0, 1, -1):
+            flib.fluke_set_lstm_persistent(2)
+            flib.fluke_sm100_set_lstm_wide(wide)
+            c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
+            out = ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh,
+                                             layer.dn_hh_scale, layer.w_up, layer.bias, c, h)
+            assert flib.fluke_sm100_lstm_last_form() == 2
+            res.append((out.clone(), c.clone(), h.clone()))
+        flib.fluke_sm100_set_lstm_wide(-1)
+        flib.fluke_set_lstm_persistent(1)
+        for other in res[1:]:
+            assert torch.equal(res[0][0], other[0]) and torch.equal(res[0][1], other[1]) and torch.equal(res[0][2], other[2])
+        he, ce, _ = _run_oracle_layer(layer, x, xs, False)
+        d = np.abs(res[1][0].cpu().numpy().astype(np.int32) - he.astype(np.int32))
+        assert d.max() <= 1 and (d != 0).mean() < 5e-3
