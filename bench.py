@@ -12,7 +12,12 @@ path). One "step" = one pass of the whole stack over one [T, B, 768] int8 batch.
     e2e              the same through the public API with HOST buffers (fluke_b200.lstm.StackPipeline):
                      every step copies its input from pinned host memory and its output back,
                      all inside the timed region; the driver overlaps the copies of neighbouring
-                     steps with the layers of the current one (pipeline fill and drain included)
+                     steps with the layers of the current one and runs two consecutive steps
+                     side by side in one layer launch (2048 chunks: the recurrence is a latency-
+                     bound chain, and the wide single-launch configuration holds 16 row tiles);
+                     pipeline fill and drain included, an odd last step runs alone
+    two_passes_per_launch   `value`'s measurement repeated with two resident batches per layer
+                     launch (what e2e does, without the copies); reported beside, not as, `value`
     roofline         the persistent LSTM recurrence kernel (tensor bound): algorithmic FLOPs per
                      launch / its launch duration, measured with CUDA events on the launching
                      stream, against the measured bf16 GEMM peak of this pool
@@ -324,7 +329,7 @@ def run_ours(args):
     # end to end: every pass copies its input from pinned host memory and its output back; the
     # passes go through the library's streaming driver, which overlaps the copies of neighbouring
     # passes with the layers of the current one
-    pipe = StackPipeline(layers, T, B, dev)
+    pipe = StackPipeline(layers, T, B, dev, passes_per_launch=2)
 
     def step_e2e():
         return pipe.submit(x_host, xs_host, out_host)
@@ -353,9 +358,26 @@ def run_ours(args):
         sampler.start()
     ms = timed(step_resident, args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    step_e2e()
+    for _ in range(3):      # a full group and a single pass: both paths of the driver warmed up
+        step_e2e()
     pipe.drain()
     ms_e2e = timed(step_e2e, args.steps, after=pipe.drain)   # fill and drain of the pipeline included
+    del pipe
+    torch.cuda.empty_cache()
+    # the resident measurement again with two batches side by side in each layer launch
+    x2, xs2 = torch.cat([x_dev, x_dev], dim=1), torch.cat([xs_dev.view(T, B)] * 2, dim=1).reshape(-1)
+    bufs2 = [torch.empty(T, 2 * B, H, dtype=torch.int8, device=dev) for _ in range(2)]
+    ws2 = torch.empty(flib.load().fluke_factored_lstm_layer_workspace(T, 2 * B, H, R), dtype=torch.uint8, device=dev)
+
+    def step_pair():
+        st = [(torch.zeros(2 * B, H, dtype=torch.float32, device=dev), torch.zeros(2 * B, H, dtype=torch.int8, device=dev))
+              for _ in range(NL)]
+        return run_stack(layers, x2, xs2, state=st, workspace=ws2, buffers=bufs2)[0]
+
+    step_pair()
+    pairs = max(1, args.steps // 2)
+    ms_pair = timed(step_pair, pairs) / 2.0                    # per pass
+    del x2, xs2, bufs2, ws2
     status = flib.read_status()
     if status != 0:
         raise SystemExit(f"bench.py: device status word {status:#x}: a bounded device wait gave up")
@@ -412,7 +434,10 @@ def run_ours(args):
                        "parallelism": f"dp{world} (independent chunks, no collective)"},
             "timesteps_per_sec_per_gpu_per_layer": T * NL / (ms * 1e-3),
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": x_host.numel() + xs_host.numel() * 4, "d2h_bytes_per_step": out_host.numel()},
+                    "h2d_bytes_per_step": x_host.numel() + xs_host.numel() * 4, "d2h_bytes_per_step": out_host.numel(),
+                    "passes_per_launch": 2},
+            "two_passes_per_launch": {"value": units / (ms_pair * 1e-3), "unit": UNIT, "ms_per_step": ms_pair,
+                                      "note": "two resident batches of 1024 chunks side by side in each layer launch"},
             "gpu_launches": args.steps * NL * 2,   # per layer: x_down GEMM + persistent recurrence
             "clocks": clocks, "roofline": roofline,
             "cpu_baseline": {"value": cpu_v, "unit": "chunk-timesteps/s (per layer)", "cores": cores, "kind": "port",
@@ -453,7 +478,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     args = ap.parse_args()
