@@ -48,6 +48,8 @@ namespace {
 constexpr int kPThreads = 320;          // warp 0 producer, warp 1 MMA, warps 2-5 / 6-9 epilogue
 constexpr int kPRank = 128;             // factor rank the kernel is built for
 constexpr int kPMaxHKB = 8;             // hidden K blocks of 128 bytes: H <= 1024
+constexpr long long kPStaggerCycles = 9000;  // head start of a pair's first row tile over its second: about
+                                        // half a step (a step is 14-19 thousand cycles); measured flat from 7 to 12 thousand
 
 struct PersistDev {
     int T, B, H;               // B: chunks handled by this launch
@@ -441,6 +443,13 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     tma_load_2d(smem + L::kOffDn + kb * L::kDnKB, &tm_dn, bar_once, kb * 128, 0);
                 bool ok = true;
                 for (int i = 0; i < p.T && ok; ++i) {
+                    if (i == 0 && (tile & 1)) {
+                        // the second tile of a pair starts about half a step late and stays there:
+                        // the two recurrences then use their gate CTA's epilogue warps' pipes (XU)
+                        // alternately instead of at the same time
+                        const long long t0 = clock64();
+                        while (clock64() - t0 < kPStaggerCycles) {}
+                    }
                     if (i > 0) {
                         ok = mbar_wait(&bar_acc_full[0], (i - 1) & 1, abort_flag, 48);  // h tile free again
                         if (!ok) break;
