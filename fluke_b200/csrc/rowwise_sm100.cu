@@ -173,13 +173,18 @@ enum { kOutF16 = 0, kOutI8 = 1, kOutF8 = 2 };
 // MODE kOutI8 : v = in + (float(res_i8)*res_scale)*alpha, int8 + scale written over the
 //               residual in place, scale = 1/(127/amax)                (nn_kernel_cuda.h:182-228)
 // MODE kOutF8 : same with e4m3 residual, scale = max(amax,1e-12)/448   (nn_kernel_cuda.h:305-345)
+// CTAs of four rows, and for hidden sizes up to 512 a register budget of 32 (16 CTAs = all 64 warps
+// of an SM resident): the kernel is a chain of dependent steps per row in short-lived warps, so
+// it lives on occupancy and on a fine CTA granularity at the tail (config 2, int8: 13.1 us with
+// 8-row CTAs at 40 registers, 12.7 with 8-row CTAs at 32, 12.5 with 4-row CTAs at 32).
+constexpr int kNormWarps = 4;
 template <int L, int MODE>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kNormWarps * 32, (L <= 2 ? 16 : 1))
 rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
                     const __half *__restrict__ weight, void *out, float *res_scale, int n_tokens,
                     int hidden_dim, float alpha, float eps) {
     const int lane = threadIdx.x & 31;
-    const int64_t row = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t row = int64_t(blockIdx.x) * kNormWarps + (threadIdx.x >> 5);
     if (row >= n_tokens) return;
     const int64_t base = row * hidden_dim;
 
@@ -390,8 +395,8 @@ int launch_rmsnorm(const void *in, const void *residual_in, const void *weight, 
         ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(weight) |
           reinterpret_cast<uintptr_t>(residual_in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
     if (hidden_dim % 256 == 0 && aligned) {
-        const int grid = (n_tokens + kWarpsPerBlock - 1) / kWarpsPerBlock;
-        const int block = kWarpsPerBlock * 32;
+        const int grid = (n_tokens + kNormWarps - 1) / kNormWarps;
+        const int block = kNormWarps * 32;
         switch (hidden_dim / 256) {
             case 1: rmsnorm_rows_kernel<1, MODE><<<grid, block, 0, s>>>(x, residual_in, w, out, res_scale, n_tokens, hidden_dim, alpha, eps); break;
             case 2: rmsnorm_rows_kernel<2, MODE><<<grid, block, 0, s>>>(x, residual_in, w, out, res_scale, n_tokens, hidden_dim, alpha, eps); break;
