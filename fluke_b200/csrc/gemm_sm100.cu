@@ -115,8 +115,7 @@ struct SmemLayout {
     static constexpr int kOffW = 0;
     static constexpr int kOffA = kWeightBytes;
     static constexpr int kOffStaging = kOffA + STAGES * kABytes;
-    static constexpr int kOffScaleB = kOffStaging + kEpilogueWarps * kStagingBytes;  // ROTARY: f32 [BN_MMA]
-    static constexpr int kOffBars = kOffScaleB + (EPI == FLUKE_SM100_EPI_ROTARY ? BN_MMA * 4 : 0);
+    static constexpr int kOffBars = kOffStaging + kEpilogueWarps * kStagingBytes;
     static constexpr int kNumBars = 2 * STAGES + 5;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kTotal = kOffMisc + 16;
@@ -143,6 +142,15 @@ __device__ __forceinline__ float acc_to_float(uint32_t bits) {
 template <int KIND>
 __device__ __forceinline__ float2 acc_to_float2(uint32_t a, uint32_t b) {
     return make_float2(acc_to_float<KIND>(a), acc_to_float<KIND>(b));
+}
+
+// Four 8 x 8 matrices of 16-bit elements, each thread giving its fragment of every matrix (the
+// two adjacent elements 2t, 2t+1 of row g) in one register: lane i supplies the shared-memory
+// address of row i % 8 of matrix i / 8 (16 bytes per row).
+__device__ __forceinline__ void stmatrix_x4(const void *row_addr, const uint32_t (&r)[4]) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                 ::"r"(smem_u32(row_addr)), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+                 : "memory");
 }
 
 // Writes one 128-byte row (8 x 16-byte chunks held in v[0..31]) into a swizzled staging tile.
@@ -202,11 +210,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         tma_prefetch_desc(&tm_out);
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
-    if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
-        // weight scales of the tile's columns, read by every epilogue thread of the rotary kernel
-        float *sbs = reinterpret_cast<float *>(smem + L::kOffScaleB);
-        for (int j = threadIdx.x; j < BN_MMA; j += kNumThreads) sbs[j] = __ldg(p.scale_b + n0 + j);
-    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -372,121 +375,128 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
             }
         } else if constexpr (EPI == FLUKE_SM100_EPI_ROTARY) {
-            // Thread = output row (32-lane x 32-bit loads). A tile is four heads; warp `ch` owns
-            // heads 2*ch and 2*ch+1. The 32 sin and 32 cos values of the row's position stay in
-            // registers: with sequence-aligned tiling they are loaded once per run of tiles with
-            // the same tile-in-sequence index, otherwise at the start of every tile.
+            // A tile is four heads; warp `ch` owns heads 2*ch and 2*ch+1. Accumulators come in the
+            // 16-lane x 256-bit layout: a thread holds columns 8j + 2t, +1 (j = 0..7) of a head for
+            // rows g + 8k (k = 0..3) of its quadrant, so both halves of a rotation pair (columns i
+            // and i + 32: j and j + 4) are its own, its 32 column scales never change (registers),
+            // and it needs 16 sin and 16 cos pairs: rows g + 8k x pair indices 8j + 2t, +1 (j < 4).
+            // Those stay in registers too: with sequence-aligned tiling they are loaded once per
+            // run of tiles with the same tile-in-sequence index, otherwise at the start of every
+            // tile. The epilogue reads nothing from shared memory; its outputs, which are 8 x 8
+            // matrix fragments in this layout, go to the staging tile four matrices per
+            // instruction (stmatrix).
             static_assert(BN_OUT == 256, "two heads per epilogue warp");
-            const float *sbs = reinterpret_cast<const float *>(smem + L::kOffScaleB);
             const bool rotate = n0 < p.qk_cols;
-            float2 sn2[16], cs2[16];  // pairs (e, e+1) as they come out of the 16-byte loads
-            auto load_tables = [&](int pos) {
-                const float4 *s4 = reinterpret_cast<const float4 *>(p.sin_tab + pos * 32);
-                const float4 *c4 = reinterpret_cast<const float4 *>(p.cos_tab + pos * 32);
+            float2 sc[2][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float4 sv = __ldg(s4 + j), cv = __ldg(c4 + j);
-                    sn2[2 * j] = make_float2(sv.x, sv.y);
-                    sn2[2 * j + 1] = make_float2(sv.z, sv.w);
-                    cs2[2 * j] = make_float2(cv.x, cv.y);
-                    cs2[2 * j + 1] = make_float2(cv.z, cv.w);
+            for (int h2 = 0; h2 < 2; ++h2)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    sc[h2][j] = __ldg(reinterpret_cast<const float2 *>(p.scale_b + n0 + (2 * ch + h2) * 64 + 8 * j + 2 * t4));
+            float2 sn2[4][4], cs2[4][4];  // [row k][pair group j]
+            auto load_tables = [&](int k, int pos) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    sn2[k][j] = __ldg(reinterpret_cast<const float2 *>(p.sin_tab + pos * 32 + 8 * j + 2 * t4));
+                    cs2[k][j] = __ldg(reinterpret_cast<const float2 *>(p.cos_tab + pos * 32 + 8 * j + 2 * t4));
                 }
             };
+            // stmatrix: lane i gives the address of row i % 8 of matrix i / 8
+            const uint32_t st_row = lane & 7, st_mat = lane >> 3;
             const bool seq_mode = p.seq_tiles > 0;
             int cur_s = -1;
-            auto load_sa1 = [&](int m0) {
-                const int row = m0 + q * 32 + lane;
-                return p.scale_a ? (row < p.M ? __ldg(p.scale_a + row) : 0.f) : p.const_scale_a;
-            };
-            float sa_next = it.w_begin < it.w_end ? load_sa1(TileIter::row0(p, it.w_begin)) : 0.f;
+            float sa_next[4];
+            if (it.w_begin < it.w_end) load_sa(TileIter::row0(p, it.w_begin), sa_next);
             for (int w = it.w_begin; w < it.w_end && ok; w += it.w_step, ++local) {
                 const int m0 = TileIter::row0(p, w);
                 const int acc = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
-                const float sa = sa_next;
-                const float2 sa2 = make_float2(sa, sa);
-                if (w + it.w_step < it.w_end) sa_next = load_sa1(TileIter::row0(p, w + it.w_step));
+                float2 sa2[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) sa2[k] = make_float2(sa_next[k], sa_next[k]);
+                if (w + it.w_step < it.w_end) load_sa(TileIter::row0(p, w + it.w_step), sa_next);
                 if (rotate) {
                     if (seq_mode) {
                         // the positions only change when the tile-in-sequence index does
                         const int s_idx = TileIter::seq_index(p, w);
                         if (s_idx != cur_s) {
                             cur_s = s_idx;
-                            load_tables(TileIter::seq_pos0(p, s_idx) + q * 32 + lane);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) load_tables(k, TileIter::seq_pos0(p, s_idx) + q * 32 + g8 + 8 * k);
                         }
                     } else {
-                        const int grow = m0 + q * 32 + lane;
-                        load_tables(grow < p.M ? grow % p.seqlen : 0);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int grow = m0 + q * 32 + g8 + 8 * k;
+                            load_tables(k, grow < p.M ? grow % p.seqlen : 0);
+                        }
                     }
                 }
 
                 ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, 4);
                 if (!ok) break;
                 tc_fence_after_sync();
-                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA;
+                const uint32_t t_base = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MMA;
 
-                // One head's 128-byte output row segment; kRot is a type so that the rotation is
-                // compiled in or out of the inner loop instead of branched around per pair.
-                auto head_math = [&](auto rot_tag, int c0, uint32_t (&outw)[32]) {
+                // One head: 64 columns x the quadrant's 32 rows, two loads of 16 rows. kRot is a
+                // type so that the rotation is compiled in or out of the inner loop.
+                auto head_math = [&](auto rot_tag, int h2) {
                     constexpr bool kRot = decltype(rot_tag)::value;
-#pragma unroll
-                    for (int sub = 0; sub < 2; ++sub) {
-                        // rotation pairs 16*sub .. 16*sub+15: columns (i, i+32) of the head
-                        uint32_t lo[16], hi[16];
-                        tmem_ld_32x16(t_row + c0 + sub * 16, lo);
-                        tmem_ld_32x16(t_row + c0 + 32 + sub * 16, hi);
-                        float4 bl4[4], bh4[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            bl4[i] = *reinterpret_cast<const float4 *>(sbs + c0 + sub * 16 + 4 * i);
-                            bh4[i] = *reinterpret_cast<const float4 *>(sbs + c0 + 32 + sub * 16 + 4 * i);
-                        }
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int e = 2 * i;
-                            // (acc*sa)*sb, then the rotation in a fixed operation order (no
-                            // compiler-chosen contraction): lo' = fma(x0, cos, -(x1*sin)),
-                            // hi' = fma(x0, sin, x1*cos)
-                            const float2 bl2 = (i & 1) ? make_float2(bl4[i >> 1].z, bl4[i >> 1].w)
-                                                       : make_float2(bl4[i >> 1].x, bl4[i >> 1].y);
-                            const float2 bh2 = (i & 1) ? make_float2(bh4[i >> 1].z, bh4[i >> 1].w)
-                                                       : make_float2(bh4[i >> 1].x, bh4[i >> 1].y);
-                            const float2 x0 = mul2(mul2(acc_to_float2<KIND>(lo[e], lo[e + 1]), sa2), bl2);
-                            const float2 x1 = mul2(mul2(acc_to_float2<KIND>(hi[e], hi[e + 1]), sa2), bh2);
-                            float2 o_lo = x0, o_hi = x1;
-                            if constexpr (kRot) {
-                                const float2 m = mul2(x1, sn2[sub * 8 + i]);
-                                o_lo = fma2(x0, cs2[sub * 8 + i], make_float2(-m.x, -m.y));
-                                o_hi = fma2(x0, sn2[sub * 8 + i], mul2(x1, cs2[sub * 8 + i]));
-                            }
-                            outw[sub * 8 + i] = pack_half2(o_lo.x, o_lo.y);
-                            outw[16 + sub * 8 + i] = pack_half2(o_hi.x, o_hi.y);
-                        }
-                    }
-                };
-#pragma unroll 1
-                for (int h2 = 0; h2 < 2; ++h2) {
                     const int c0 = (2 * ch + h2) * 64;  // first column of the head inside the tile
-                    uint32_t outw[32];
-                    if (rotate) head_math(TrueTag{}, c0, outw);
-                    else head_math(FalseTag{}, c0, outw);
-                    if (h2 == 1) {
-                        // Every TMEM read of this accumulator is done: hand it back to the MMA
-                        // warp before the slower store path.
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+#pragma unroll
+                    for (int hr = 0; hr < 2; ++hr) {  // rows g, g+8 then g+16, g+24
+                        uint32_t a[32];
+                        tmem_ld_16x256_x8(t_base + (uint32_t(16 * hr) << 16) + c0, a);
+                        tmem_ld_wait();
+                        if (h2 == 1 && hr == 1) {
+                            // Every TMEM read of this accumulator is done: hand it back to the MMA
+                            // warp before the arithmetic and the store.
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+                        }
+                        if (hr == 0) {
+                            // the store of the previous head must have read the staging tile
+                            if (lane == 0) tma_store_wait_read<0>();
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int k2 = 0; k2 < 2; ++k2) {
+                            const int k = 2 * hr + k2;
+                            uint32_t wlo[4], whi[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                // (acc*sa)*sb, then the rotation in a fixed operation order (no
+                                // compiler-chosen contraction): lo' = fma(x0, cos, -(x1*sin)),
+                                // hi' = fma(x0, sin, x1*cos)
+                                const float2 x0 = mul2(mul2(acc_to_float2<KIND>(a[4 * j + 2 * k2], a[4 * j + 2 * k2 + 1]), sa2[k]), sc[h2][j]);
+                                const float2 x1 = mul2(mul2(acc_to_float2<KIND>(a[4 * (j + 4) + 2 * k2], a[4 * (j + 4) + 2 * k2 + 1]), sa2[k]),
+                                                       sc[h2][j + 4]);
+                                float2 o_lo = x0, o_hi = x1;
+                                if constexpr (kRot) {
+                                    const float2 m = mul2(x1, sn2[k][j]);
+                                    o_lo = fma2(x0, cs2[k][j], make_float2(-m.x, -m.y));
+                                    o_hi = fma2(x0, sn2[k][j], mul2(x1, cs2[k][j]));
+                                }
+                                wlo[j] = pack_half2(o_lo.x, o_lo.y);
+                                whi[j] = pack_half2(o_hi.x, o_hi.y);
+                            }
+                            // rows 8k .. 8k+7 of the quadrant: column chunks 0-3, then 4-7
+                            stmatrix_x4(staging + sw128_offset(8 * k + st_row, st_mat), wlo);
+                            stmatrix_x4(staging + sw128_offset(8 * k + st_row, 4 + st_mat), whi);
+                        }
                     }
-                    if (lane == 0) tma_store_wait_read<0>();
-                    __syncwarp();
-                    stage_row(staging, lane, outw);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
                         tma_store_2d(&tm_out, staging, n0 + c0, m0 + q * 32);
                         tma_store_commit();
                     }
+                };
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    if (rotate) head_math(TrueTag{}, h2);
+                    else head_math(FalseTag{}, h2);
                 }
             }
         } else {
