@@ -331,11 +331,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 sa[k] = p.scale_a ? (row < p.M ? __ldg(p.scale_a + row) : 0.f) : p.const_scale_a;
             }
         };
-        // 4-byte store of two adjacent f16 outputs (columns 8j + 2t, +1 of the 64-column staging
-        // tile) of quadrant row r; conflict-free: the 8 rows of an instruction hit 8 chunks
-        auto stage_pair = [&](int r, int j, uint32_t v) {
-            *reinterpret_cast<uint32_t *>(staging + sw128_offset(r, j) + 4 * t4) = v;
-        };
 
         if constexpr (EPI == FLUKE_SM100_EPI_RAW) {
             // 32-bit accumulators, no scaling: thread = row, 32 columns per store
@@ -556,6 +551,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 #pragma unroll
                     for (int k2 = 0; k2 < 2; ++k2) {
                         const int k = 2 * hr + k2;
+                        uint32_t wv[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float2 v = acc_to_float2<KIND>(a[4 * j + 2 * k2], a[4 * j + 2 * k2 + 1]);
@@ -572,8 +568,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             } else {
                                 o = mul2(mul2(v, sa2[k]), sc[j]);
                             }
-                            stage_pair(g8 + 8 * k, j, pack_half2(o.x, o.y));
+                            wv[j] = pack_half2(o.x, o.y);
                         }
+                        // the eight 8 x 8 fragments of rows 8k .. 8k+7: four matrices per instruction
+                        const uint32_t lo4[4] = {wv[0], wv[1], wv[2], wv[3]}, hi4[4] = {wv[4], wv[5], wv[6], wv[7]};
+                        stmatrix_x4(staging + sw128_offset(8 * k + (lane & 7), lane >> 3), lo4);
+                        stmatrix_x4(staging + sw128_offset(8 * k + (lane & 7), 4 + (lane >> 3)), hi4);
                     }
                 }
                 if (!cols_ok) continue;
