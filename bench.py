@@ -258,6 +258,12 @@ def bench_ops(torch, peaks):
     s8 = [torch.ones(n, device=dev) for _ in range(6)]
     ms = time_rotating([lambda i=i: ops.rmsnorm_quant_int8(xs_[i], w, q8[i], s8[i], 0.0, 1e-5) for i in range(6)], 20, torch)
     out["rmsnorm_quant_int8_cfg2"] = entry(ms, 65.79e6)
+    # per-row quantisers on the same [32000,512] f16 input: read 2 B, write 1 B per element + scales
+    u8 = [torch.zeros(n, h, dtype=torch.uint8, device=dev) for _ in range(6)]
+    ms = time_rotating([lambda i=i: ops.quant_int8(xs_[i], out=q8[i], scale=s8[i]) for i in range(6)], 20, torch)
+    out["quant_int8_cfg2"] = entry(ms, n * h * 3 + n * 4)
+    ms = time_rotating([lambda i=i: ops.quant_fp8(xs_[i], out=u8[i], scale=s8[i]) for i in range(6)], 20, torch)
+    out["quant_fp8_cfg2"] = entry(ms, n * h * 3 + n * 4)
     # config 3: QKV int8 GEMM + rotary, M=32000
     be = ops.int8_select(0)
     a8 = [prep.quantize_int8_rows(torch.randn(n, 512, generator=g)) for _ in range(3)]

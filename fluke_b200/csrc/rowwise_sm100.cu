@@ -62,6 +62,19 @@ __device__ __forceinline__ uint8_t e4m3_encode(float f) {
     return uint8_t(sign | m);
 }
 
+// Two values at once with the conversion instruction. The instruction rounds to nearest even,
+// the software encoder above (the reference's) rounds half away from zero: setting the lowest
+// mantissa bit of the f32 input moves an exact tie (an even bit pattern, whatever the exponent)
+// just above the tie and never carries another value across one, so the results agree for every
+// finite input; both saturate at +-448 and flush what is below half the smallest subnormal to a
+// signed zero. Byte 0 of the result encodes `lo`, byte 1 `hi`.
+__device__ __forceinline__ uint32_t e4m3_encode_pair(float lo, float hi) {
+    uint16_t r;
+    const float a = __uint_as_float(__float_as_uint(hi) | 1u), b = __uint_as_float(__float_as_uint(lo) | 1u);
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(a), "f"(b));
+    return r;
+}
+
 // ---- small helpers -----------------------------------------------------------------------
 __device__ __forceinline__ void unpack8(const uint4 &raw, float2 (&f)[4]) {
     const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
@@ -281,14 +294,13 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
 #pragma unroll
         for (int q = 0; q < L; ++q) {
             const int off = (q * 32 + lane) * 8;
-            uint2 raw;
-            uint8_t *ob = reinterpret_cast<uint8_t *>(&raw);
+            uint32_t hw[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                ob[2 * k] = e4m3_encode(fmaxf(-448.0f, fminf(448.0f, val[q][k].x / fp8_scale)));
-                ob[2 * k + 1] = e4m3_encode(fmaxf(-448.0f, fminf(448.0f, val[q][k].y / fp8_scale)));
-            }
-            *reinterpret_cast<uint2 *>(static_cast<uint8_t *>(out) + base + off) = raw;
+            for (int k = 0; k < 4; ++k)
+                hw[k] = e4m3_encode_pair(fmaxf(-448.0f, fminf(448.0f, val[q][k].x / fp8_scale)),
+                                         fmaxf(-448.0f, fminf(448.0f, val[q][k].y / fp8_scale)));
+            *reinterpret_cast<uint2 *>(static_cast<uint8_t *>(out) + base + off) =
+                make_uint2(hw[0] | (hw[1] << 16), hw[2] | (hw[3] << 16));
         }
     }
 }
@@ -408,6 +420,59 @@ int launch_rmsnorm(const void *in, const void *residual_in, const void *weight, 
         rmsnorm_generic_kernel<MODE><<<n_tokens, block, 0, s>>>(x, residual_in, w, out, res_scale, n_tokens, hidden_dim, alpha, eps);
     }
     return (int)cudaGetLastError();
+}
+
+// ---- per-token quantisers (nn_kernel_cuda.h:352-411), hidden_dim = 256*L: one warp per row, the
+// row stays in registers between the maximum and the conversion. int8: round(v * inv) by magic
+// addition after clamping to +-127 in float (the same integers as rounding first), bytes gathered
+// with permutes; e4m3: the conversion instruction. CTA shape as for the RMSNorm kernels.
+template <int L, bool FP8>
+__global__ void __launch_bounds__(kNormWarps * 32, (L <= 2 ? 16 : 1))
+quant_rows_reg_kernel(const __half *__restrict__ in, uint8_t *__restrict__ out,
+                      float *__restrict__ scale, int n_tokens) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = int64_t(blockIdx.x) * kNormWarps + (threadIdx.x >> 5);
+    if (row >= n_tokens) return;
+    const int64_t base = row * (256 * L);
+    float2 val[L][4];
+    float amax = 0.f;
+#pragma unroll
+    for (int q = 0; q < L; ++q) {
+        unpack8(__ldg(reinterpret_cast<const uint4 *>(in + base + (q * 32 + lane) * 8)), val[q]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) amax = fmaxf(amax, fmaxf(fabsf(val[q][k].x), fabsf(val[q][k].y)));
+    }
+    amax = warp_max(amax);
+    const float dq = fmaxf(amax, 1e-12f) / (FP8 ? 448.0f : 128.0f);
+    if (lane == 0) scale[row] = dq;
+    const float inv = 1.0f / dq;
+    const float2 inv2 = make_float2(inv, inv);
+#pragma unroll
+    for (int q = 0; q < L; ++q) {
+        uint2 raw;
+        if constexpr (FP8) {
+            uint32_t h[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 pv = mul2(val[q][k], inv2);
+                h[k] = e4m3_encode_pair(fmaxf(-448.0f, fminf(448.0f, pv.x)), fmaxf(-448.0f, fminf(448.0f, pv.y)));
+            }
+            raw = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+        } else {
+            uint32_t t[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 pv = mul2(val[q][k], inv2);
+                const float2 cl = make_float2(fmaxf(-127.0f, fminf(127.0f, pv.x)), fmaxf(-127.0f, fminf(127.0f, pv.y)));
+                // c * 1 + 1.5 * 2^23 rounds the clamped product to an integer in the low mantissa bits
+                const float2 rq = fma2(cl, make_float2(1.0f, 1.0f), make_float2(12582912.0f, 12582912.0f));
+                t[2 * k] = __float_as_uint(rq.x);
+                t[2 * k + 1] = __float_as_uint(rq.y);
+            }
+            raw = make_uint2(pack_low_bytes(t[0], t[1], t[2], t[3]), pack_low_bytes(t[4], t[5], t[6], t[7]));
+        }
+        *reinterpret_cast<uint2 *>(out + base + (q * 32 + lane) * 8) = raw;
+    }
 }
 
 // ---- per-token quantisers (nn_kernel_cuda.h:352-411): one warp per row, any even H ----------
@@ -712,6 +777,23 @@ static int launch_quant(const void *in, void *out, void *scale, int n_tokens, in
     const int vec_ok = (hidden_dim % 8 == 0) &&
                        ((reinterpret_cast<uintptr_t>(in) & 15u) == 0) &&
                        ((reinterpret_cast<uintptr_t>(out) & 7u) == 0);
+    if (vec_ok && hidden_dim % 256 == 0 && hidden_dim <= 1024) {
+        const __half *x = static_cast<const __half *>(in);
+        uint8_t *o = static_cast<uint8_t *>(out);
+        float *sc = static_cast<float *>(scale);
+        const int grid = (n_tokens + kNormWarps - 1) / kNormWarps, block = kNormWarps * 32;
+        switch ((hidden_dim / 256) * 2 + (fp8 ? 1 : 0)) {
+            case 2: quant_rows_reg_kernel<1, false><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+            case 3: quant_rows_reg_kernel<1, true><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+            case 4: quant_rows_reg_kernel<2, false><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+            case 5: quant_rows_reg_kernel<2, true><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+            case 6: quant_rows_reg_kernel<3, false><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+            case 7: quant_rows_reg_kernel<3, true><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+            case 8: quant_rows_reg_kernel<4, false><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+            default: quant_rows_reg_kernel<4, true><<<grid, block, 0, s>>>(x, o, sc, n_tokens); break;
+        }
+        return (int)cudaGetLastError();
+    }
     const int grid = (n_tokens + kWarpsPerBlock - 1) / kWarpsPerBlock;
     if (fp8)
         quant_rows_kernel<true><<<grid, kWarpsPerBlock * 32, 0, s>>>(

@@ -64,18 +64,22 @@ def rmsnorm_quant_fp8(x, weight, residual_u8, residual_scale, alpha, eps):
     return residual_u8, residual_scale
 
 
-def quant_int8(x):
+def quant_int8(x, out=None, scale=None):
     _dev(x)
-    out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
-    scale = torch.empty(x.size(0), dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    if scale is None:
+        scale = torch.empty(x.size(0), dtype=torch.float32, device=x.device)
     _L().fluke_quant_int8_gpu(_p(x), _p(out), _p(scale), x.size(0), x.size(1))
     return out, scale
 
 
-def quant_fp8(x):
+def quant_fp8(x, out=None, scale=None):
     _dev(x)
-    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
-    scale = torch.empty(x.size(0), dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    if scale is None:
+        scale = torch.empty(x.size(0), dtype=torch.float32, device=x.device)
     _L().fluke_quant_fp8_gpu(_p(x), _p(out), _p(scale), x.size(0), x.size(1))
     return out, scale
 

@@ -107,6 +107,31 @@ def test_rmsnorm_family_side_by_side(n, h):
     assert torch.equal(a8, b8) and same_bits(as_, bs)
 
 
+def test_fp8_quantiser_rounds_ties_like_the_reference_encoder():
+    """The reference's e4m3 encoder rounds a value half-way between two codes away from zero; the
+    conversion instruction the row kernel uses rounds such ties to even and is therefore fed with
+    the lowest mantissa bit set. Rows whose maximum is 448 have scale 1, so the inputs below reach
+    the encoder unchanged: every f16 value that lies exactly between two e4m3 codes (normal and
+    subnormal range, both signs), its f16 neighbours, and the saturating end."""
+    codes = port.e4m3_decode_table()[:0x7F].astype(np.float64)          # positive finite codes, ascending
+    mids = (codes[:-1] + codes[1:]) / 2
+    mids = mids[mids.astype(np.float16).astype(np.float64) == mids]      # exactly representable in f16
+    near = np.concatenate([np.nextafter(mids.astype(np.float16), np.float16(0)).astype(np.float64),
+                           np.nextafter(mids.astype(np.float16), np.float16(1000)).astype(np.float64)])
+    vals = np.concatenate([mids, near, codes, [2.0 ** -10, 2.0 ** -11, 3 * 2.0 ** -11, 447.0, 440.0, 432.0]])
+    vals = np.concatenate([vals, -vals]).astype(np.float16)
+    for h in (512, 384):                                                  # register path and generic path
+        n = (vals.size + h - 2) // (h - 1)
+        x = np.zeros((n, h), dtype=np.float16)
+        x[:, 0] = 448.0
+        flat = np.zeros(n * (h - 1), dtype=np.float16)
+        flat[:vals.size] = vals
+        x[:, 1:] = flat.reshape(n, h - 1)
+        f, fs = ops.quant_fp8(torch.from_numpy(x).to(DEV))
+        assert np.all(fs.cpu().numpy() == 1.0)
+        assert np.array_equal(f.cpu().numpy(), port.e4m3_encode(x.astype(np.float32)))
+
+
 @pytest.mark.parametrize("n,h", [(300, 512), (128, 1024), (64, 2048), (512, 512), (9, 6), (1000, 1000)])
 def test_quantisers_side_by_side(n, h):
     R = _ref()
