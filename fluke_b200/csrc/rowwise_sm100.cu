@@ -62,6 +62,18 @@ __device__ __forceinline__ uint8_t e4m3_encode(float f) {
     return uint8_t(sign | m);
 }
 
+// Four codes at once with the conversion instruction (e4m3 values are exact in f16). The software
+// decoder above gives +0 for the NaN codes and for -0: those bytes are cleared first.
+__device__ __forceinline__ void e4m3x4_decode(uint32_t word, float2 &lo, float2 &hi) {
+    const uint32_t mag = word & 0x7F7F7F7Fu;
+    word &= ~(__vcmpeq4(mag, 0x7F7F7F7Fu) | __vcmpeq4(mag, 0u));
+    uint32_t h01, h23;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(uint16_t(word & 0xFFFFu)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"(uint16_t(word >> 16)));
+    lo = __half22float2(*reinterpret_cast<const __half2 *>(&h01));
+    hi = __half22float2(*reinterpret_cast<const __half2 *>(&h23));
+}
+
 // Two values at once with the conversion instruction. The instruction rounds to nearest even,
 // the software encoder above (the reference's) rounds half away from zero: setting the lowest
 // mantissa bit of the f32 input moves an exact tie (an even bit pattern, whatever the exponent)
@@ -221,7 +233,6 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
         } else {
             const uint2 raw = *reinterpret_cast<const uint2 *>(
                 static_cast<const uint8_t *>(residual_in) + base + off);
-            const uint8_t *rb = reinterpret_cast<const uint8_t *>(&raw);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 if constexpr (MODE == kOutI8) {
@@ -231,9 +242,10 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
                     // reference's build contracts to), two elements per instruction
                     val[q][k] = fma2(mul2(r, make_float2(rs, rs)), make_float2(alpha, alpha), xf[k]);
                 } else {
-                    const float r0 = e4m3_decode(rb[2 * k]);
-                    const float r1 = e4m3_decode(rb[2 * k + 1]);
-                    val[q][k] = make_float2(xf[k].x + r0 * rs * alpha, xf[k].y + r1 * rs * alpha);
+                    float2 ra, rb2;
+                    e4m3x4_decode((k < 2) ? raw.x : raw.y, ra, rb2);
+                    const float2 r = (k & 1) ? rb2 : ra;
+                    val[q][k] = make_float2(xf[k].x + r.x * rs * alpha, xf[k].y + r.y * rs * alpha);
                 }
             }
         }
@@ -718,10 +730,22 @@ dequant_transpose_kernel(const uint8_t *__restrict__ in, __half *__restrict__ ou
         const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(src));
         const uint8_t *rb = reinterpret_cast<const uint8_t *>(&raw);
         float2 f0[4], f1[4];
+        if constexpr (FP8) {
+            e4m3x4_decode(raw.x, f0[0], f0[1]);
+            e4m3x4_decode(raw.y, f0[2], f0[3]);
+            e4m3x4_decode(raw.z, f1[0], f1[1]);
+            e4m3x4_decode(raw.w, f1[2], f1[3]);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            f0[k] = make_float2(deq(rb[2 * k]), deq(rb[2 * k + 1]));
-            f1[k] = make_float2(deq(rb[8 + 2 * k]), deq(rb[8 + 2 * k + 1]));
+            for (int k = 0; k < 4; ++k) {
+                f0[k] = make_float2(f0[k].x * scale, f0[k].y * scale);
+                f1[k] = make_float2(f1[k].x * scale, f1[k].y * scale);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                f0[k] = make_float2(deq(rb[2 * k]), deq(rb[2 * k + 1]));
+                f1[k] = make_float2(deq(rb[8 + 2 * k]), deq(rb[8 + 2 * k + 1]));
+            }
         }
         reinterpret_cast<uint4 *>(dst)[0] = pack8(f0);
         reinterpret_cast<uint4 *>(dst)[1] = pack8(f1);
