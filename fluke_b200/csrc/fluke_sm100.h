@@ -62,6 +62,12 @@ int fluke_sm100_fp8_unshuffle(void *dst_nk, const void *src, int N, int K, void 
  * 128 x n x 32 bytes (kind 0 int8, 1 e4m3, 2 f16) on shared-memory-resident operands and write
  * their SM-clock cycle counts to cycles_dev[0 .. n_ctas) (device, int64). */
 int fluke_sm100_mma_peak(int kind, int n, int iters, void *cycles_dev, int n_ctas, void *stream);
+/* Strided copy between pinned host memory and the device by the copy engine alone (no staging
+ * buffer, no kernel): `height` rows of `width` bytes, pitches in bytes. to_device != 0: host ->
+ * device, else device -> host. For drivers that place a batch beside another one in a wider
+ * device tensor. */
+int fluke_sm100_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
+                                size_t width, size_t height, int to_device, void *stream);
 
 /* ---- tcgen05 GEMM family ---------------------------------------------------------------- */
 

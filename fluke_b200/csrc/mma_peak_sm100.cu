@@ -75,3 +75,10 @@ extern "C" int fluke_sm100_mma_peak(int kind, int n, int iters, void *cycles_dev
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
+
+extern "C" int fluke_sm100_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
+                                           size_t width, size_t height, int to_device, void *stream) {
+    return (int)cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, height,
+                                  to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
+                                  static_cast<cudaStream_t>(stream));
+}

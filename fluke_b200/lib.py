@@ -79,6 +79,7 @@ SIGNATURES = {
     # internal status word (bounded device waits)
     "fluke_sm100_read_status": (I, [ctypes.POINTER(ctypes.c_uint), I]),
     "fluke_sm100_mma_peak": (I, [I, I, I, P, I, P]),
+    "fluke_sm100_copy_rows_async": (I, [P, ctypes.c_size_t, P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, I, P]),
     "fluke_sm100_lstm_last_form": (I, []),
     "fluke_sm100_set_lstm_wide": (None, [I]),
     "fluke_sm100_lstm_cluster_capacity": (I, [I]),

@@ -215,15 +215,16 @@ def test_layer_config_size_properties(lstm_mode):
         assert torch.equal(h3, fwd[0])
 
 
-@pytest.mark.parametrize("passes_per_launch", [1, 2])
-def test_streaming_pipeline_equals_pass_by_pass(passes_per_launch):
+@pytest.mark.parametrize("passes_per_launch,time_chunks", [(1, 1), (2, 1), (2, 3), (1, 4)])
+def test_streaming_pipeline_equals_pass_by_pass(passes_per_launch, time_chunks):
     """Five passes with different inputs through the three-stream driver (copy-in, layers,
     copy-out overlapped across groups of passes) give the bytes of run_stack on each input alone;
-    with two passes per launch the fifth is a group of its own that `drain` runs."""
+    with two passes per launch the fifth is a group of its own that `drain` runs; with time chunks
+    the first and the last layer run block by block between their copies."""
     T, B, H, R, NL = 6, 200, 768, 128, 3
     g = torch.Generator().manual_seed(77)
     layers = [FactoredLstmLayer.random(H, R, bool(i % 2), g, DEV) for i in range(NL)]
-    pipe = StackPipeline(layers, T, B, DEV, passes_per_launch=passes_per_launch)
+    pipe = StackPipeline(layers, T, B, DEV, passes_per_launch=passes_per_launch, time_chunks=time_chunks)
     ins, outs = [], []
     for k in range(5):
         x, xs = prep.quantize_int8_rows(torch.randn(T * B, H, generator=g))
