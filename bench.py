@@ -385,7 +385,25 @@ def run_ours(args):
     step_pair()
     pairs = max(1, args.steps // 2)
     ms_pair = timed(step_pair, pairs) / 2.0                    # per pass
-    del x2, xs2, bufs2, ws2
+    # its recurrence kernel (the wide configuration: 16 row tiles in one launch), timed like the
+    # headline kernel below: layer minus x_down GEMM
+    lay0 = layers[0]
+    st2 = (torch.zeros(2 * B, H, dtype=torch.float32, device=dev), torch.zeros(2 * B, H, dtype=torch.int8, device=dev))
+
+    def layer2(mask):
+        ops.factored_lstm_layer_i8(x2, xs2, lay0.dn_ih, lay0.dn_ih_scale, lay0.dn_hh, lay0.dn_hh_scale, lay0.w_up,
+                                   lay0.bias, st2[0], st2[1], h_out=bufs2[0], workspace=ws2, phase_mask=mask)
+    us_pair = {}
+    for mask in (7, 1):
+        layer2(mask)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        layer2(mask); layer2(mask)
+        e1.record()
+        torch.cuda.synchronize()
+        us_pair[mask] = e0.elapsed_time(e1) / 2 * 1e3
+    del x2, xs2, bufs2, ws2, st2
     status = flib.read_status()
     if status != 0:
         raise SystemExit(f"bench.py: device status word {status:#x}: a bounded device wait gave up")
@@ -445,7 +463,11 @@ def run_ours(args):
                     "h2d_bytes_per_step": x_host.numel() + xs_host.numel() * 4, "d2h_bytes_per_step": out_host.numel(),
                     "passes_per_launch": 2, "time_chunks": 4},
             "two_passes_per_launch": {"value": units / (ms_pair * 1e-3), "unit": UNIT, "ms_per_step": ms_pair,
-                                      "note": "two resident batches of 1024 chunks side by side in each layer launch"},
+                                      "note": "two resident batches of 1024 chunks side by side in each layer launch",
+                                      "recurrence_kernel_us": round(us_pair[7] - us_pair[1], 3),
+                                      "recurrence_kernel_tflops": round(2 * flops / ((us_pair[7] - us_pair[1]) * 1e-6) / 1e12, 2),
+                                      "recurrence_kernel_frac": round(2 * flops / ((us_pair[7] - us_pair[1]) * 1e-6) / 1e12
+                                                                      / peaks["tf_sustained"], 4)},
             "gpu_launches": args.steps * NL * 2,   # per layer: x_down GEMM + persistent recurrence
             "clocks": clocks, "roofline": roofline,
             "cpu_baseline": {"value": cpu_v, "unit": "chunk-timesteps/s (per layer)", "cores": cores, "kind": "port",

@@ -215,6 +215,28 @@ def test_layer_config_size_properties(lstm_mode):
         assert torch.equal(h3, fwd[0])
 
 
+def test_two_batches_side_by_side_config_size(flib):
+    """Two benchmark-size batches (2 x 1024 chunks, H = 768, R = 128; T cut to 24) in one layer
+    call, which the wide L2-exchange configuration runs in a single launch of 16 row tiles, give
+    the bytes of the two batches run on their own (narrow configuration, 8 row tiles each)."""
+    T, B, H, R = 24, 1024, 768, 128
+    flib.fluke_set_lstm_persistent(2)
+    layer, x, xs = _layer_case(T, 2 * B, H, R, 9, True)
+    X, XS = x.to(DEV), xs.to(DEV)
+    args = (layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale, layer.w_up, layer.bias)
+    c = torch.zeros(2 * B, H, device=DEV); h = torch.zeros(2 * B, H, dtype=torch.int8, device=DEV)
+    both = ops.factored_lstm_layer_i8(X, XS, *args, c, h, reverse=True).clone()
+    assert flib.fluke_sm100_lstm_last_form() == 2
+    for j in range(2):
+        xj = X[:, j * B:(j + 1) * B].contiguous()
+        xsj = XS.view(T, 2 * B)[:, j * B:(j + 1) * B].contiguous().view(-1)
+        cj = torch.zeros(B, H, device=DEV); hj = torch.zeros(B, H, dtype=torch.int8, device=DEV)
+        one = ops.factored_lstm_layer_i8(xj, xsj, *args, cj, hj, reverse=True)
+        assert torch.equal(one, both[:, j * B:(j + 1) * B])
+        assert torch.equal(cj, c[j * B:(j + 1) * B]) and torch.equal(hj, h[j * B:(j + 1) * B])
+    flib.fluke_set_lstm_persistent(1)
+
+
 @pytest.mark.parametrize("passes_per_launch,time_chunks", [(1, 1), (2, 1), (2, 3), (1, 4)])
 def test_streaming_pipeline_equals_pass_by_pass(passes_per_launch, time_chunks):
     """Five passes with different inputs through the three-stream driver (copy-in, layers,
