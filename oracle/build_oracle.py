@@ -1,6 +1,6 @@
 """Build the test oracles. TEST INFRASTRUCTURE ONLY (never imported by the product path).
 
-    python oracle/build_oracle.py [--ref-dir /root/reference]
+    python oracle/build_oracle.py [--ref-dir <reference checkout>]
 
 1. oracle/liboracle.so     the CPU restatement oracle/fluke_oracle.c (gcc, OpenMP,
                            -ffp-contract=off so only the explicit fmaf() calls fuse).
