@@ -113,29 +113,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
 }
 
-// The same wait for warps that can afford a few tens of nanoseconds of wake-up delay: between
-// attempts the thread sleeps, so that the attempts of many waiting warps do not compete with the
-// tensor core's operand reads for the shared-memory pipe (a 128 x 128 x 32-byte MMA reads 8 KB in
-// 64 cycles: all of the pipe's 128 bytes per cycle).
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                                  unsigned int site, unsigned int sleep_ns = 64) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i) {
-            __nanosleep(sleep_ns);
-            if (mbar_try_wait(bar, parity)) return true;
-        }
-        if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycleLimit) {
-            report_timeout(site);
-            *abort_flag = 1;
-            return false;
-        }
-    }
-}
-
 // ---------------------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), 2-D and 3-D tiles; loads complete on an mbarrier, stores are
 // tracked with bulk groups.
