@@ -451,7 +451,8 @@ int launch_rmsnorm(const void *in, const void *residual_in, const void *weight, 
 // ---- per-token quantisers (nn_kernel_cuda.h:352-411), hidden_dim = 256*L: one warp per row, the
 // row stays in registers between the maximum and the conversion. int8: round(v * inv) by magic
 // addition after clamping to +-127 in float (the same integers as rounding first), bytes gathered
-// with permutes; e4m3: the conversion instruction. CTA shape as for the RMSNorm kernels.
+// with permutes (a NaN input, which the reference's conversion maps to 0, becomes 127 here); e4m3:
+// the conversion instruction. CTA shape as for the RMSNorm kernels.
 template <int L, bool FP8>
 __global__ void __launch_bounds__(kNormWarps * 32, (L <= 2 ? 16 : 1))
 quant_rows_reg_kernel(const __half *__restrict__ in, uint8_t *__restrict__ out,
