@@ -132,7 +132,7 @@ def test_fp8_quantiser_rounds_ties_like_the_reference_encoder():
         assert np.array_equal(f.cpu().numpy(), port.e4m3_encode(x.astype(np.float32)))
 
 
-@pytest.mark.parametrize("n,h", [(300, 512), (128, 1024), (64, 2048), (512, 512), (9, 6), (1000, 1000)])
+@pytest.mark.parametrize("n,h", [(300, 512), (128, 1024), (64, 2048), (512, 512), (9, 6), (1000, 1000), (32000, 512), (77, 768), (5, 256)])
 def test_quantisers_side_by_side(n, h):
     R = _ref()
     x = (torch.randn(n, h, generator=torch.Generator().manual_seed(n * h)) * 3).half().to(DEV)
