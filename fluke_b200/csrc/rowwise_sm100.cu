@@ -641,6 +641,19 @@ rotary_scalar_kernel(__half *x, const float *__restrict__ sin_tab,
     *o1 = __float2half(__fmaf_rn(x0, sin, __fmul_rn(x1, cos)));
 }
 
+// idx -> (idx / per_row, idx % per_row): a 32-bit division where the index allows it (a 64-bit one
+// costs about as many instructions as the arithmetic of the element-wise kernels below).
+__device__ __forceinline__ void split_index(int64_t idx, int64_t total, int per_row, int64_t &row, int &col) {
+    if (total < (int64_t(1) << 31)) {
+        const uint32_t i32 = uint32_t(idx), r32 = i32 / uint32_t(per_row);
+        row = r32;
+        col = int(i32 - r32 * uint32_t(per_row));
+    } else {
+        row = idx / per_row;
+        col = int(idx % per_row);
+    }
+}
+
 // ---- SiLU-multiply (nn_kernel_cuda.h:71-90) -----------------------------------------------------
 template <int VEC>
 __global__ void __launch_bounds__(256)
@@ -649,8 +662,10 @@ silu_mul_kernel(const __half *__restrict__ in, __half *__restrict__ out, int64_t
     const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total_vec) return;
     const int per_row = hidden_dim / VEC;
-    const int64_t t = idx / per_row;
-    const int k = int(idx % per_row) * VEC;
+    int64_t t;
+    int k;
+    split_index(idx, total_vec, per_row, t, k);
+    k *= VEC;
     const __half *y = in + t * 2 * hidden_dim + k;
     const __half *g = y + hidden_dim;
     __half *o = out + t * hidden_dim + k;
@@ -691,8 +706,10 @@ flstm_step_kernel(const __half *__restrict__ scratch, const __half *__restrict__
     const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total_vec) return;
     const int per_row = hidden_dim / VEC;
-    const int64_t n = idx / per_row;
-    const int ch = int(idx % per_row) * VEC;
+    int64_t n;
+    int ch;
+    split_index(idx, total_vec, per_row, n, ch);
+    ch *= VEC;
     const int64_t gbase = n * 4 * hidden_dim + ch, cbase = n * hidden_dim + ch;
     if constexpr (VEC == 8) {
         float2 a[4][4], b[4][4], cf[4], cn[4], hn[4];
@@ -732,9 +749,11 @@ dequant_transpose_kernel(const uint8_t *__restrict__ in, __half *__restrict__ ou
     const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total_vec) return;
     const int per_row = n_channels / VEC;
-    const int64_t tn = idx / per_row;
-    const int c = int(idx % per_row) * VEC;
-    const int64_t t = tn / batch_size, n = tn - t * batch_size;
+    int64_t tn, t;
+    int c, n;
+    split_index(idx, total_vec, per_row, tn, c);
+    c *= VEC;
+    split_index(tn, total_vec, batch_size, t, n);
     const uint8_t *src = in + tn * n_channels + c;
     __half *dst = out + (n * n_timesteps + t) * n_channels + c;
     auto deq = [&](uint8_t b) -> float {
