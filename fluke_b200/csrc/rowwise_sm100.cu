@@ -100,6 +100,16 @@ __device__ __forceinline__ float div_by_scale(float x, float s, float r) {
     return __uint_as_float((__float_as_uint(q) & 0x7FFFFFFFu) | (__float_as_uint(x) & 0x80000000u));
 }
 
+// The same for two values in packed arithmetic.
+__device__ __forceinline__ float2 div_by_scale2(float2 x, float s, float r) {
+    const float2 s2 = make_float2(-s, -s), r2 = make_float2(r, r);
+    float2 q = mul2(x, r2);
+    q = fma2(fma2(q, s2, x), r2, q);
+    q = fma2(fma2(q, s2, x), r2, q);
+    return make_float2(__uint_as_float((__float_as_uint(q.x) & 0x7FFFFFFFu) | (__float_as_uint(x.x) & 0x80000000u)),
+                       __uint_as_float((__float_as_uint(q.y) & 0x7FFFFFFFu) | (__float_as_uint(x.y) & 0x80000000u)));
+}
+
 // ---- small helpers -----------------------------------------------------------------------
 __device__ __forceinline__ void unpack8(const uint4 &raw, float2 (&f)[4]) {
     const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
@@ -257,8 +267,8 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
                 } else {
                     float2 ra, rb2;
                     e4m3x4_decode((k < 2) ? raw.x : raw.y, ra, rb2);
-                    const float2 r = (k & 1) ? rb2 : ra;
-                    val[q][k] = make_float2(xf[k].x + r.x * rs * alpha, xf[k].y + r.y * rs * alpha);
+                    // x + (r * rs) * alpha as for the int8 residual: product, then one fused multiply-add
+                    val[q][k] = fma2(mul2((k & 1) ? rb2 : ra, make_float2(rs, rs)), make_float2(alpha, alpha), xf[k]);
                 }
             }
         }
@@ -323,8 +333,10 @@ rmsnorm_rows_kernel(const __half *__restrict__ in, const void *residual_in,
             uint32_t hw[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                hw[k] = e4m3_encode_pair(fmaxf(-448.0f, fminf(448.0f, div_by_scale(val[q][k].x, fp8_scale, fp8_rcp))),
-                                         fmaxf(-448.0f, fminf(448.0f, div_by_scale(val[q][k].y, fp8_scale, fp8_rcp))));
+            {
+                const float2 dv = div_by_scale2(val[q][k], fp8_scale, fp8_rcp);
+                hw[k] = e4m3_encode_pair(fmaxf(-448.0f, fminf(448.0f, dv.x)), fmaxf(-448.0f, fminf(448.0f, dv.y)));
+            }
             *reinterpret_cast<uint2 *>(static_cast<uint8_t *>(out) + base + off) =
                 make_uint2(hw[0] | (hw[1] << 16), hw[2] | (hw[3] << 16));
         }
