@@ -47,10 +47,17 @@ endif
 SM100_SRC = fluke_b200/csrc/fluke_sm100_all.cu
 SM100_DEPS = $(wildcard fluke_b200/csrc/*.cu fluke_b200/csrc/*.cuh fluke_b200/csrc/*.h)
 
-.PHONY: all shared clean distclean
+PROBELIB = $(BUILD_DIR)/libfluke_probe.so
+
+.PHONY: all shared probe clean distclean
 
 all: $(STATICLIB)
 shared: $(SHAREDLIB)
+# tcgen05 issue-rate probe the benchmark compares the GEMM kernels with; not part of libfluke
+probe: $(PROBELIB)
+
+$(PROBELIB): fluke_b200/csrc/mma_peak_sm100.cu $(SM100_DEPS) | $(BUILD_DIR)
+	$(NVCC) $(CUDA_CFLAGS) $(CPPFLAGS) -shared fluke_b200/csrc/mma_peak_sm100.cu -o $@ $(CUDA_LDFLAGS)
 
 $(STATICLIB): $(OBJ) $(GPU_OBJ)
 	rm -f $@

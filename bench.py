@@ -204,10 +204,7 @@ def measure_tensor_peaks(torch):
     kernels are quoted against these."""
     import ctypes
     from fluke_b200 import lib as flib
-    L = flib.load()
-    fn = L.fluke_sm100_mma_peak
-    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
-    fn.restype = ctypes.c_int
+    fn = flib.load_probe().fluke_sm100_mma_peak
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     cyc = torch.zeros(sms, dtype=torch.int64, device="cuda")
     out = {}

@@ -32,6 +32,9 @@ int fluke_sm100_read_status(unsigned int *status_out, int reset);
 /* Device allocation for the one place the library keeps private memory (the re-ordered fp8
  * weight copies). */
 int fluke_sm100_malloc(void **ptr, size_t bytes);
+int fluke_sm100_free(void *ptr);
+/* Index of the calling thread's current device, -1 when it cannot be queried. */
+int fluke_sm100_current_device(void);
 
 /* ---- memory-bound row kernels (bit-compatible with the reference's pure-CUDA kernels) --- */
 
@@ -58,9 +61,10 @@ int fluke_sm100_flstm_step(const void *scratch, const void *ih_t, void *cell, vo
                            int batch_size, int hidden_dim, void *stream);
 int fluke_sm100_fp8_unshuffle(void *dst_nk, const void *src, int N, int K, void *stream);
 
-/* tcgen05.mma issue-rate probe: n_ctas CTAs each time `iters` back-to-back MMAs of shape
- * 128 x n x 32 bytes (kind 0 int8, 1 e4m3, 2 f16) on shared-memory-resident operands and write
- * their SM-clock cycle counts to cycles_dev[0 .. n_ctas) (device, int64). */
+/* tcgen05.mma issue-rate probe (lib/libfluke_probe.so, not libfluke): n_ctas CTAs each time
+ * `iters` back-to-back MMAs of shape 128 x n x 32 bytes (kind 0 int8, 1 e4m3, 2 f16) on
+ * shared-memory-resident operands and write their SM-clock cycle counts to cycles_dev[0 .. n_ctas)
+ * (device, int64). */
 int fluke_sm100_mma_peak(int kind, int n, int iters, void *cycles_dev, int n_ctas, void *stream);
 /* Strided copy between pinned host memory and the device by the copy engine alone (no staging
  * buffer, no kernel): `height` rows of `width` bytes, pitches in bytes. to_device != 0: host ->
@@ -130,10 +134,15 @@ int fluke_sm100_lstm_layer(const void *layer /* const fluke_flstm_layer_t* */, v
 /* Launch only some kernel classes of the layer: 1 = x_down GEMM, 2 = per-step down-projection,
  * 4 = per-step fused step (7 = the layer). For timing one class alone. */
 int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, void *stream);
-/* 1 (default): run the recurrence of a layer as one launch, with the exchange inside thread-block
- * clusters where shape and device allow (R = 128, H a multiple of 64 up to 768), else through L2
- * (R = 128, H a multiple of 128 up to 1024); 2: the L2-exchange form only; 0: always two launches
- * per timestep. */
+/* How the recurrence of a layer is run (a per-host-thread setting).
+ * 1 (default): one launch, the fastest single-launch form the shape and the device allow: the
+ *    cluster form while all row tiles of the layer run at once, else the L2-exchange form, else the
+ *    cluster form in rounds;
+ * 2: the L2-exchange form only (separate projection CTAs; R = 128, H a multiple of 128 up to 1024);
+ * 4: the cluster form only, in rounds when the layer has more row tiles than clusters fit
+ *    (exchange inside thread-block clusters; R = 128, H a multiple of 64 up to 768);
+ * 0: two launches per timestep.
+ * A form that does not cover the shape falls back to the next one that does. */
 void fluke_sm100_set_lstm_persistent(int mode);
 /* Configuration of the L2-exchange form. Narrow: 24 or 32 hidden units per gate CTA, two workers
  * per row tile (8 row tiles per launch on 148 SMs at H = 768). Wide: 48 units per gate CTA, one

@@ -7,4 +7,4 @@
 #include "lstm_persist_sm100.cu"
 #include "lstm_cluster_sm100.cu"
 #include "lstm_noalloc_sm100.cu"
-#include "mma_peak_sm100.cu"
+#include "stack_sm100.cu"

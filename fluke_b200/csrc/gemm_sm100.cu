@@ -786,6 +786,15 @@ extern "C" int fluke_sm100_compute_capability(int device_index) {
 extern "C" int fluke_sm100_malloc(void **ptr, size_t bytes) {
     return (int)cudaMalloc(ptr, bytes);
 }
+// Waits for the device's outstanding work before releasing (cudaFree does), so a kernel still
+// reading the block finishes first.
+extern "C" int fluke_sm100_free(void *ptr) {
+    return (int)cudaFree(ptr);
+}
+extern "C" int fluke_sm100_current_device(void) {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+}
 
 extern "C" const char *fluke_sm100_error_string(int code) {
     return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -58,7 +58,7 @@ struct ClusterDev {
     const float *dn_scale;     // [R]
     float *c;                  // [B,H]
     int8_t *h_out;             // [T,B,H]
-    long long *trace;          // optional [T][8] nanosecond stamps of tile 0's first gate and projection CTA
+    long long *trace;          // trace builds only: [T][8] nanosecond stamps of tile 0's first gate and projection CTA
 };
 
 struct ClusterSmem {
@@ -245,7 +245,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                             tc_mma<kKindF16>(tmem_base, ad + uint64_t(2 * k), bd + uint64_t(2 * k), kIdesc, 1u);
                     }
                     if (ok) tc_commit(bar_acc_full);
-                    if (p.trace && blockIdx.x == 0) p.trace[i * 8 + 0] = global_ns();
+                    FLUKE_STAMP(blockIdx.x == 0, i * 8 + 0, global_ns());
                 }
             }
             __syncwarp();
@@ -277,7 +277,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             for (int i = 0; i < p.T && ok; ++i) {
                 ok = mbar_wait(bar_acc_full, i & 1, abort_flag, 75);
                 if (!ok) break;
-                if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) p.trace[i * 8 + 1] = global_ns();
+                FLUKE_STAMP(blockIdx.x == 0 && threadIdx.x == 64, i * 8 + 1, global_ns());
                 tc_fence_after_sync();
                 uint32_t packed[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
@@ -318,13 +318,13 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     fence_proxy_async_smem();
                     ok = warps_barrier(bar_epi, (i + 1) & 1, lane, abort_flag);
                     if (ok && e == 0 && lane == 0) {
-                        if (p.trace && blockIdx.x == 0) p.trace[i * 8 + 2] = global_ns();
+                        FLUKE_STAMP(blockIdx.x == 0, i * 8 + 2, global_ns());
                         const uint32_t dst = smem_u32(smem + L::kOffH + rank * 8192);
                         const uint32_t bar = smem_u32(&bar_h[rank]);
                         for (int wk = 0; wk < kCWorkers; ++wk)
                             push_to_peer(map_to_rank(dst, p.n_slices + wk), shs, 8192,
                                          map_to_rank(bar, p.n_slices + wk));
-                        if (p.trace && blockIdx.x == 0) p.trace[i * 8 + 3] = global_ns();
+                        FLUKE_STAMP(blockIdx.x == 0, i * 8 + 3, global_ns());
                     }
                 }
                 if (row_ok)
@@ -375,7 +375,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                                             (j | k) != 0 ? 1u : 0u);
                     }
                     if (ok) tc_commit(bar_acc_full);
-                    if (p.trace && int(blockIdx.x) == p.n_slices) p.trace[i * 8 + 4] = global_ns();
+                    FLUKE_STAMP(int(blockIdx.x) == p.n_slices, i * 8 + 4, global_ns());
                 }
             }
             __syncwarp();
@@ -396,7 +396,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
             for (int i = 0; i < p.T && ok; ++i) {
                 ok = mbar_wait(bar_acc_full, i & 1, abort_flag, 83);
                 if (!ok) break;
-                if (p.trace && int(blockIdx.x) == p.n_slices && threadIdx.x == 64) p.trace[i * 8 + 5] = global_ns();
+                FLUKE_STAMP(int(blockIdx.x) == p.n_slices && threadIdx.x == 64, i * 8 + 5, global_ns());
                 tc_fence_after_sync();
                 uint32_t acc[32];
                 tmem_ld_32x32(t_row, acc);
@@ -420,12 +420,12 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                 fence_proxy_async_smem();
                 ok = warps_barrier(bar_epi, i & 1, lane, abort_flag);
                 if (ok && warp == 2 && lane == 0) {
-                    if (p.trace && int(blockIdx.x) == p.n_slices) p.trace[i * 8 + 6] = global_ns();
+                    FLUKE_STAMP(int(blockIdx.x) == p.n_slices, i * 8 + 6, global_ns());
                     const uint32_t dst = smem_u32(smem + L::kOffAhh + widx * 8192);
                     const uint32_t bar = smem_u32(&bar_ahh[widx]);
                     for (int s = 0; s < p.n_slices; ++s)
                         push_to_peer(map_to_rank(dst, s), sout, 8192, map_to_rank(bar, s));
-                    if (p.trace && int(blockIdx.x) == p.n_slices) p.trace[i * 8 + 7] = global_ns();
+                    FLUKE_STAMP(int(blockIdx.x) == p.n_slices, i * 8 + 7, global_ns());
                 }
             }
         }
@@ -516,7 +516,7 @@ extern "C" int fluke_sm100_lstm_layer_cluster(const void *layer, const void *x_d
     p.dn_scale = static_cast<const float *>(l->dn_hh_scale);
     p.c = static_cast<float *>(l->c_f32);
     p.h_out = static_cast<int8_t *>(l->h_out_i8);
-    p.trace = g_persist_trace;
+    p.trace = trace_buffer();
 
     CUtensorMap tm_w[4], tm_x, tm_dn, tm_h0;
     int rc;

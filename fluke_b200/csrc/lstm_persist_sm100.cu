@@ -63,12 +63,17 @@ struct PersistDev {
     int8_t *h_out;             // [T,B,H]
     __half *hh_down;           // [B,R]
     unsigned int *flags;       // [0,n_tiles): h_ready, [n_tiles,2n_tiles): hh_ready, [2n_tiles]: abort
-    long long *trace;          // optional [T][8] SM-clock stamps of CTA 0 and of the first worker
+    long long *trace;          // trace builds only: [T][8] SM-clock stamps of CTA 0 and of the first worker
 };
 
-// Development aid: when a trace buffer is set, the first gate CTA and the first worker CTA
-// record clock64() at the hand-over points of every step.
+// Builds with -DFLUKE_SM100_TRACE (never the library's default build) record time stamps at the
+// hand-over points of every step into a buffer set with fluke_sm100_lstm_set_trace.
+#ifdef FLUKE_SM100_TRACE
 static long long *g_persist_trace = nullptr;
+inline long long *trace_buffer() { return g_persist_trace; }
+#else
+inline long long *trace_buffer() { return nullptr; }
+#endif
 
 // UNITS: hidden units per gate CTA. WPT: worker CTAs per row tile, 2 (each takes 64 of the
 // tile's rows) or 1 (the whole tile; for the wide configuration, where the SMs go to twice as
@@ -294,7 +299,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         ok = wait_counter(p.flags + p.n_tiles + tile, (unsigned)(WPT * (i + 1)),
                                           g_abort, abort_flag, 33);
                         if (!ok) break;
-                        if (p.trace && blockIdx.x == 0 && g == 0) p.trace[i * 8 + 0] = clock64();
+                        FLUKE_STAMP(blockIdx.x == 0 && g == 0, i * 8 + 0, clock64());
                         fence_proxy_async_all();
                         uint8_t *sa = smem + L::kOffAhh + g * 32768;
                         mbar_arrive_expect_tx(&bar_ahh[g], 32768);
@@ -330,7 +335,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                 for (int g = 0; g < n_local && ok; ++g) {  // hh_down halves: W K blocks 0, 1
                     ok = mbar_wait(&bar_ahh[g], i & 1, abort_flag, 37);
                     if (!ok) break;
-                    if (p.trace && blockIdx.x == 0 && g == 0 && lane == 0) p.trace[i * 8 + 1] = clock64();
+                    FLUKE_STAMP(blockIdx.x == 0 && g == 0 && lane == 0, i * 8 + 1, clock64());
                     tc_fence_after_sync();
                     if (lane == 0) {
                         const uint8_t *sa = smem + L::kOffAhh + g * 32768;
@@ -378,7 +383,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                 for (int i = 0; i < p.T && ok; ++i) {
                     ok = mbar_wait(&bar_acc_full[g], i & 1, abort_flag, 38);
                     if (!ok) break;
-                    if (p.trace && blockIdx.x == 0 && threadIdx.x == 64) p.trace[i * 8 + 2] = clock64();
+                    FLUKE_STAMP(blockIdx.x == 0 && threadIdx.x == 64, i * 8 + 2, clock64());
                     tc_fence_after_sync();
                     int8_t *hrow = p.h_out + (int64_t(time_of(i)) * p.b_stride + row) * p.H + n0;
 #pragma unroll
@@ -417,9 +422,9 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                     // publish this slice of h_t
                     ok = warps_barrier(&bar_epi[g], i & 1, lane, abort_flag);
                     if (ok && q == 2 && lane == 0) {
-                        if (p.trace && blockIdx.x == 0 && g == 0) p.trace[i * 8 + 3] = clock64();
+                        FLUKE_STAMP(blockIdx.x == 0 && g == 0, i * 8 + 3, clock64());
                         publish(h_ready);
-                        if (p.trace && blockIdx.x == 0 && g == 0) p.trace[i * 8 + 7] = clock64();
+                        FLUKE_STAMP(blockIdx.x == 0 && g == 0, i * 8 + 7, clock64());
                     }
                 }
                 if (row_ok) {
@@ -455,7 +460,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         if (!ok) break;
                         ok = wait_counter(h_ready, (unsigned)(p.n_slices * i), g_abort, abort_flag, 49);
                         if (!ok) break;
-                        if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 4] = clock64();
+                        FLUKE_STAMP(int(blockIdx.x) == n_gate, i * 8 + 4, clock64());
                         fence_proxy_async_all();
                     }
                     // ONE instruction for the worker's rows of the whole tile: the map walks the K
@@ -519,7 +524,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                 for (int i = 0; i < p.T && ok; ++i) {
                     ok = mbar_wait(&bar_acc_full[0], i & 1, abort_flag, 53);
                     if (!ok) break;
-                    if (p.trace && int(blockIdx.x) == n_gate && threadIdx.x == 128) p.trace[i * 8 + 5] = clock64();
+                    FLUKE_STAMP(int(blockIdx.x) == n_gate && threadIdx.x == 128, i * 8 + 5, clock64());
                     tc_fence_after_sync();
                     uint32_t acc0[32], acc1[32];
                     tmem_ld_32x32(t_row, acc0);
@@ -550,7 +555,7 @@ lstm_persist_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_cons
                         tma_store_commit();
                         tma_store_wait_all<0>();
                         publish(hh_ready);
-                        if (p.trace && int(blockIdx.x) == n_gate) p.trace[i * 8 + 6] = clock64();
+                        FLUKE_STAMP(int(blockIdx.x) == n_gate, i * 8 + 6, clock64());
                     }
                 }
             }
@@ -593,7 +598,7 @@ int persist_launch(const fluke_flstm_layer_t *l, const __half *x_down, __half *h
     p.h_out = static_cast<int8_t *>(l->h_out_i8) + size_t(b0) * H;
     p.hh_down = hh_down + size_t(b0) * R;
     p.flags = flags;
-    p.trace = g_persist_trace;
+    p.trace = trace_buffer();
 
     CUtensorMap tm_w[4], tm_x, tm_hh, tm_dn, tm_h, tm_h0, tm_hh_st;
     int rc;
@@ -667,14 +672,16 @@ int persist_max_tiles(int H) {
 }  // namespace
 }  // namespace fluke_sm100
 
+#ifdef FLUKE_SM100_TRACE
 extern "C" void fluke_sm100_lstm_set_trace(void *device_buffer) {
     fluke_sm100::g_persist_trace = static_cast<long long *>(device_buffer);
 }
+#endif
 
 // -1: the wide configuration (48 units per gate CTA, one worker per row tile: twice the row tiles
 // per launch) is used when the layer has more row tiles than one launch of the narrow one holds;
 // 0: never; 1: whenever the shape allows it.
-static int g_lstm_wide = -1;
+static thread_local int g_lstm_wide = -1;  // per host thread, like the form selection
 extern "C" void fluke_sm100_set_lstm_wide(int mode) { g_lstm_wide = mode < 0 ? -1 : (mode > 0 ? 1 : 0); }
 
 // Runs the recurrence of one layer (x_down already computed) with persistent launches. Returns

@@ -300,21 +300,25 @@ extern "C" int fluke_sm100_lstm_layer_persistent(const void *layer, const void *
                                                  void *flags, void *stream);
 extern "C" int fluke_sm100_lstm_layer_cluster(const void *layer, const void *x_down, int allow_waves,
                                               void *stream);
-// 0: two launches per timestep; 1: the fastest single-launch form the shape and device allow
-// (cluster exchange while all row tiles of the layer fit on the device at once, else L2
-// exchange); 2: the L2-exchange form only.
-static int g_lstm_last_form = -1;  // form the last whole-layer call used: 0, 1 (cluster) or 2 (L2)
+// Form selection (see fluke_sm100_set_lstm_persistent in fluke_sm100.h) and the form the last
+// whole-layer call used: 0 per step, 1 cluster, 2 L2 exchange. Both are kept per host thread: a
+// process that drives several GPUs from several threads sets and reads its own.
+static thread_local int g_lstm_last_form = -1;
 extern "C" int fluke_sm100_lstm_last_form(void) { return g_lstm_last_form; }
-static int g_lstm_persistent = 1;
-extern "C" void fluke_sm100_set_lstm_persistent(int mode) { g_lstm_persistent = mode < 0 ? 0 : (mode > 2 ? 1 : mode); }
+static thread_local int g_lstm_persistent = 1;
+extern "C" void fluke_sm100_set_lstm_persistent(int mode) { g_lstm_persistent = (mode == 0 || mode == 2 || mode == 4) ? mode : 1; }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Workspace layout: hh_down f16 [B,R] | x_down f16 [T,B,R] | 1 KB of exchange counters.
+static size_t lstm_ws_off_flags(int T, int B, int R) {
+    return align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024);
+}
 
 extern "C" size_t fluke_sm100_lstm_layer_workspace(int T, int B, int H, int R) {
     (void)H;
     if (T <= 0 || B <= 0 || R <= 0) return 0;
-    // hh_down f16 [B,R], x_down f16 [T,B,R], then 1 KB of exchange counters
-    return align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024) + 1024;
+    return lstm_ws_off_flags(T, B, R) + 1024;
 }
 
 // phase_mask selects which kernel classes are launched: 1 = x_down GEMM, 2 = per-step
@@ -351,19 +355,28 @@ extern "C" int fluke_sm100_lstm_layer_phases(const void *layer, int phase_mask, 
         if (rc) return rc;
     }
 
-    // 2. the recurrence in persistent launches where the shape allows it
+    // 2. the recurrence in one launch where a single-launch form covers the shape. Order of
+    //    preference per mode; a form answers -2 when it does not cover the shape.
     if (phase_mask == 7 && g_lstm_persistent) {
-        void *flags = ws + align_up(size_t(B) * R * 2, 1024) + align_up(size_t(T) * B * R * 2, 1024);
-        // cluster exchange when all row tiles run at once; else L2 exchange; else clusters in rounds
-        rc = g_lstm_persistent == 1 ? fluke_sm100_lstm_layer_cluster(l, x_down, 0, stream) : -2;
-        g_lstm_last_form = 1;
-        if (rc == -2) {
-            rc = fluke_sm100_lstm_layer_persistent(l, x_down, hh_down, flags, stream);
-            g_lstm_last_form = 2;
+        uint8_t *flags = ws + lstm_ws_off_flags(T, B, R);
+        auto run_form = [&](int form) -> int {
+            switch (form) {
+                case 1: return fluke_sm100_lstm_layer_cluster(l, x_down, 0, stream);   // all tiles at once only
+                case 5: return fluke_sm100_lstm_layer_cluster(l, x_down, 1, stream);   // in rounds if need be
+                case 2: return fluke_sm100_lstm_layer_persistent(l, x_down, hh_down, flags, stream);
+                default: return -2;
+            }
+        };
+        int order[4] = {0, 0, 0, 0};
+        switch (g_lstm_persistent) {
+            case 2: order[0] = 2; break;
+            case 4: order[0] = 5; order[1] = 2; break;
+            default: order[0] = 1; order[1] = 2; order[2] = 5; break;
         }
-        if (rc == -2 && g_lstm_persistent == 1) {
-            rc = fluke_sm100_lstm_layer_cluster(l, x_down, 1, stream);
-            g_lstm_last_form = 1;
+        rc = -2;
+        for (int i = 0; i < 4 && rc == -2 && order[i]; ++i) {
+            rc = run_form(order[i]);
+            g_lstm_last_form = order[i] == 5 ? 1 : order[i];
         }
         if (rc == 0) {
             const int t_last = l->reverse ? 0 : T - 1;

@@ -3,6 +3,8 @@
 // cover bf16 through cuBLAS). Every SM runs one CTA that issues `iters` back-to-back MMAs of
 // shape 128 x N x 32 bytes on operand tiles resident in shared memory (contents irrelevant:
 // zeros) and times them with clock64; no global traffic is involved.
+// Built on its own into lib/libfluke_probe.so (`make probe cuda=1`) for the benchmark; it is not
+// part of libfluke.
 #include "fluke_sm100.h"
 #include "sm100_ptx.cuh"
 
@@ -74,11 +76,4 @@ extern "C" int fluke_sm100_mma_peak(int kind, int n, int iters, void *cycles_dev
     }
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
-}
-
-extern "C" int fluke_sm100_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
-                                           size_t width, size_t height, int to_device, void *stream) {
-    return (int)cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, height,
-                                  to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
-                                  static_cast<cudaStream_t>(stream));
 }

@@ -22,6 +22,15 @@ __device__ __forceinline__ void report_timeout(unsigned int site) {
     atomicCAS(&g_status, 0u, 1u | (site << 8));
 }
 
+// Time stamps for stage tables: compiled in only with -DFLUKE_SM100_TRACE. `p` is the kernel's
+// parameter block with a `trace` pointer.
+#ifdef FLUKE_SM100_TRACE
+#define FLUKE_STAMP(cond, slot, now) \
+    do { if (p.trace && (cond)) p.trace[(slot)] = (now); } while (0)
+#else
+#define FLUKE_STAMP(cond, slot, now) do {} while (0)
+#endif
+
 // ---------------------------------------------------------------------------------------
 // Addresses, election, fences
 // ---------------------------------------------------------------------------------------

@@ -29,6 +29,11 @@ class fluke_flstm_layer_t(ctypes.Structure):
     ]
 
 
+class fluke_flstm_weights_t(ctypes.Structure):
+    _fields_ = [("dn_ih_i8", P), ("dn_ih_scale", P), ("dn_hh_i8", P), ("dn_hh_scale", P),
+                ("w_up_f16", P), ("bias_f32", P), ("reverse", I)]
+
+
 # name -> (restype, argtypes). The first ten are exactly fluke_lib._SIGNATURES of the reference.
 VOID_SIGNATURES = {
     "fluke_rotary_emb_gpu": [P, P, P, I, I, I, I, I, I, I, I],
@@ -76,9 +81,16 @@ SIGNATURES = {
     "fluke_factored_lstm_layer_i8_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t)]),
     "fluke_factored_lstm_layer_phases_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t), I]),
     "fluke_factored_lstm_layer_i8_noalloc_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t)]),
+    "fluke_factored_lstm_stack_i8_gpu": (I, [ctypes.POINTER(fluke_flstm_weights_t), I, I, I, I, I, P, P, P, P, P, P, P, Z]),
+    "fluke_flstm_stream_create": (P, [ctypes.POINTER(fluke_flstm_weights_t), I, I, I, I, I, I, I]),
+    "fluke_flstm_stream_submit": (I, [P, P, P, P, I]),
+    "fluke_flstm_stream_flush": (I, [P]),
+    "fluke_flstm_stream_drain": (I, [P]),
+    "fluke_flstm_stream_destroy": (None, [P]),
+    "fluke_fp8_prepare_weight": (I, [P, I, I]),
+    "fluke_fp8_release_weight": (I, [P]),
     # internal status word (bounded device waits)
     "fluke_sm100_read_status": (I, [ctypes.POINTER(ctypes.c_uint), I]),
-    "fluke_sm100_mma_peak": (I, [I, I, I, P, I, P]),
     "fluke_sm100_copy_rows_async": (I, [P, ctypes.c_size_t, P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, I, P]),
     "fluke_sm100_lstm_last_form": (I, []),
     "fluke_sm100_set_lstm_wide": (None, [I]),
@@ -88,9 +100,12 @@ for _n, _a in VOID_SIGNATURES.items():
     SIGNATURES[_n] = (None, _a)
 
 
+PROBE_PATH = os.path.join(ROOT, "lib", "libfluke_probe.so")
+
+
 def build(verbose=False):
-    """`make shared cuda=1` at the repository root (nvcc cross-compiles sm_100a without a GPU)."""
-    cmd = ["make", "shared", "cuda=1"]
+    """`make shared probe cuda=1` at the repository root (nvcc cross-compiles sm_100a without a GPU)."""
+    cmd = ["make", "shared", "probe", "cuda=1"]
     res = subprocess.run(cmd, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if verbose or res.returncode != 0:
         print(res.stdout)
@@ -116,6 +131,21 @@ def load(rebuild=False):
         fn.argtypes = argtypes
     _LIB = lib
     return lib
+
+
+_PROBE = None
+
+
+def load_probe():
+    """The tcgen05 issue-rate probe the benchmark uses (lib/libfluke_probe.so; not part of libfluke)."""
+    global _PROBE
+    if _PROBE is None:
+        if not os.path.isfile(PROBE_PATH):
+            build()
+        _PROBE = ctypes.CDLL(PROBE_PATH)
+        _PROBE.fluke_sm100_mma_peak.restype = I
+        _PROBE.fluke_sm100_mma_peak.argtypes = [I, I, I, P, I, P]
+    return _PROBE
 
 
 def read_status(reset=True):

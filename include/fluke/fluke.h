@@ -280,9 +280,11 @@ int fluke_gated_mlp_fp8_gpu(
  * Part 5 -- additive entry points (no prototype in the reference header).
  * ---------------------------------------------------------------------------------- */
 
-/* Stream used by every later launch of this library in the process (a cudaStream_t
- * passed as void*). NULL selects the legacy default stream, which is what the reference
- * always uses (src/nn_cuda.c launches with <<<grid, block>>>). */
+/* Stream used by every later launch this library makes FROM THE CALLING HOST THREAD (a
+ * cudaStream_t passed as void*; the setting is thread-local, so threads that each drive their own
+ * GPU or stream do not disturb one another). NULL, the initial value in every thread, selects the
+ * legacy default stream, which is what the reference always uses (src/nn_cuda.c launches with
+ * <<<grid, block>>>). Launches go to the calling thread's current CUDA device. */
 void  fluke_set_stream(void *cuda_stream);
 void *fluke_get_stream(void);
 
@@ -292,7 +294,7 @@ const char *fluke_last_error(void);
 /* Base int8 GEMM: out f16 [M,N] = f16( float(int32(a @ b^T)) * (sa[m]*scale_b[n]) ) with
  * a [M,K], b [N,K] row-major int8; sa[m] = scale_a[m], or const_scale_a when scale_a is
  * NULL. Replaces TensorOpGemmI8 (cute/ampere/gemm/gemm_i8_quant.py:182-809, scale
- * arithmetic :617 and :750). K % 16 == 0, N % 8 == 0. */
+ * arithmetic :617 and :750). K % 16 == 0, K <= 1024, N % 64 == 0. */
 int fluke_gemm_i8_gpu(
     void *out_f16, const void *a_i8, const void *b_i8,
     const void *scale_a, float const_scale_a, const void *scale_b,
@@ -313,6 +315,20 @@ int fluke_gemm_fp8_gpu(
  * preshuffle_b_fp8 produces, fly/rdna4/gemm/rdna_fp8_preshuffle_gemm.py:40-54) into
  * row-major [N, K]. */
 int fluke_fp8_unshuffle_gpu(void *dst_nk, const void *src_preshuffled, int N, int K);
+
+/* The reference-ABI fp8 entry points (fluke_qkv_rotary_fp8_gpu, fluke_gated_mlp_fp8_gpu) keep a
+ * private row-major copy of every PRESHUFFLED weight they are given, made on the first call that
+ * sees the weight's (device, address, N, K) -- one cudaMalloc and one re-ordering kernel, so that
+ * first call must not sit inside a stream capture. The copy is found again by the weight's
+ * ADDRESS: a caller that frees a weight, or writes new contents to the same address, must call
+ * fluke_fp8_release_weight before using that address again, or the stale copy is used.
+ *   fluke_fp8_prepare_weight   makes the copy now (at model load). 0 on success.
+ *   fluke_fp8_release_weight   drops the copy of one weight, or of all when passed NULL (it waits
+ *                              for the device before freeing). Returns the number dropped.
+ * The table holds 64 weights per process; beyond that the oldest copy is dropped to make room.
+ * Thread-safe. */
+int fluke_fp8_prepare_weight(const void *preshuffled, int N, int K);
+int fluke_fp8_release_weight(const void *preshuffled);
 
 /* fp8 fused ops taking plain row-major [N, K] weights (no private copy is made). */
 int fluke_qkv_rotary_fp8_plain_gpu(
@@ -376,23 +392,72 @@ typedef struct {
 size_t fluke_factored_lstm_layer_workspace(int T, int B, int H, int R);
 int fluke_factored_lstm_layer_i8_gpu(const fluke_flstm_layer_t *layer);
 
-/* How fluke_factored_lstm_layer_i8_gpu runs the recurrence.
- *   1 (default): one launch per layer, gate weights in shared memory and the cell state in
- *      registers for all T timesteps. Where the shape allows (R = 128, H a multiple of 64 up to
- *      768) and the device can hold one cluster of H/64 + 4 thread blocks per 128-chunk row tile
- *      at once (7 tiles on a B200), h / hh_down are exchanged through distributed shared memory;
- *      otherwise (R = 128, H a multiple of 128 up to 1024) through L2 with per-tile counters.
- *   2: the L2-exchange form only.
- *   0: always two launches per timestep.
- * All give the same int8 outputs within one code (the two K halves are accumulated in a
- * different order). */
+/* How fluke_factored_lstm_layer_i8_gpu runs the recurrence (a per-thread setting).
+ *   1 (default): one launch per layer -- gate weights in shared memory and the cell state in
+ *      registers for all T timesteps -- in the fastest form the shape and the device allow.
+ *   2: exchange through L2 with separate projection thread blocks (R = 128, H a multiple of 128
+ *      up to 1024).
+ *   4: exchange inside thread-block clusters through distributed shared memory (R = 128, H a
+ *      multiple of 64 up to 768; 7 row tiles of 128 chunks at a time on a B200).
+ *   0: two launches per timestep.
+ * A form that does not cover the shape falls back to one that does. The single-launch forms give
+ * identical bytes; the per-step kernels the same int8 outputs within one code (the two K halves
+ * are accumulated in the other order, tanh by the library routine). */
 void fluke_set_lstm_persistent(int mode);
 
-/* Measurement aid: launch only some kernel classes of the layer so one class can be timed
- * alone. phase_mask bits: 1 = x_down GEMM, 2 = per-step down-projection, 4 = per-step fused
- * step; 7 is fluke_factored_lstm_layer_i8_gpu. With any other mask the outputs are not a
- * layer result. */
-int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int phase_mask);
+/* ---- whole stack ---------------------------------------------------------------------------
+ * The loop around the layer that slorado's CRFModel runs (README.md:82-92; the loop itself is
+ * not part of the reference checkout): layers applied in order, layer 0 on per-row quantised
+ * input (x_scale), every later layer on the previous layer's int8 hidden output at the fixed
+ * scale 1/127, each walking time forwards or backwards as its `reverse` says. */
+typedef struct {
+    const void *dn_ih_i8;       /* [R,H] int8   */
+    const void *dn_ih_scale;    /* f32 [R]      */
+    const void *dn_hh_i8;       /* [R,H] int8   */
+    const void *dn_hh_scale;    /* f32 [R]      */
+    const void *w_up_f16;       /* [4*H, 2*R] f16, as in fluke_flstm_layer_t */
+    const void *bias_f32;       /* [4*H] f32    */
+    int reverse;
+} fluke_flstm_weights_t;
+
+/* One pass of the stack over device buffers, on the calling thread's stream; allocates nothing.
+ * x_i8 [T,B,H] with x_scale f32 [T*B] (or NULL = 1/127); out_i8 [T,B,H] receives the last
+ * layer's hidden outputs; scratch_i8 [T,B,H] is a second buffer the layers alternate with (may
+ * be NULL for a single layer; x_i8 is not written). c_f32 [n_layers,B,H] and h_i8 [n_layers,B,H]
+ * hold every layer's state, in (initial) and out (final). workspace as for one layer. */
+int fluke_factored_lstm_stack_i8_gpu(
+    const fluke_flstm_weights_t *layers, int n_layers, int T, int B, int H, int R,
+    const void *x_i8, const void *x_scale, void *out_i8, void *scratch_i8,
+    void *c_f32, void *h_i8, void *workspace, size_t workspace_bytes
+);
+
+/* Host-to-host streaming of many passes of a stack. The handle owns its device buffers (two input
+ * sets, two output buffers, two layer buffers, state and workspace: about 6 x T*P*B*H bytes) and
+ * three streams: while one group of passes runs the layers, the inputs of the next are copied in
+ * and the outputs of the one before copied out.
+ *   create   passes_per_launch = P >= 1 puts P consecutive passes side by side in one batch of
+ *            P*B chunks and runs each layer once over it (chunks are independent: the same
+ *            bytes); time_chunks = C >= 1 runs the first and the last layer in C calls over
+ *            consecutive blocks of timesteps so that a group's copies overlap its own layers.
+ *            Allocates on the calling thread's current device. NULL on failure.
+ *   submit   x_host_i8 [T,B,H], x_scale_host f32 [T*B] and out_host_i8 [T,B,H] are PINNED host
+ *            buffers that stay valid until drain. zero_state != 0: the pass starts from c = 0,
+ *            h = 0. Only enqueues work. A group is launched when it is full or when nothing is
+ *            running.
+ *   flush    launches a group that is only partly filled.
+ *   drain    flush, then blocks until every submitted pass's output is in its host buffer.
+ *   destroy  waits for outstanding work and frees everything.
+ * One host thread per handle. int functions return 0 or a CUDA error code. */
+typedef struct fluke_flstm_stream fluke_flstm_stream_t;
+fluke_flstm_stream_t *fluke_flstm_stream_create(
+    const fluke_flstm_weights_t *layers, int n_layers, int T, int B, int H, int R,
+    int passes_per_launch, int time_chunks
+);
+int  fluke_flstm_stream_submit(fluke_flstm_stream_t *s, const void *x_host_i8, const void *x_scale_host,
+                               void *out_host_i8, int zero_state);
+int  fluke_flstm_stream_flush(fluke_flstm_stream_t *s);
+int  fluke_flstm_stream_drain(fluke_flstm_stream_t *s);
+void fluke_flstm_stream_destroy(fluke_flstm_stream_t *s);
 
 /* No counterpart in the reference. The same layer as fluke_factored_lstm_layer_i8_gpu for
  * callers that cannot allocate device memory (inside a stream capture, plug-ins without an

@@ -5,7 +5,8 @@
  * The ABI passes weights PRESHUFFLED as [N/16, K/16, 2, 16, 8] bytes, which neither TMA nor a
  * UMMA shared-memory descriptor can address as a K-major operand, so the first call that sees
  * a weight pointer re-orders it once into a private row-major [N, K] device copy; later calls
- * find it in a small pointer-keyed table. The *_plain_gpu variants take row-major weights and
+ * find it in a small pointer-keyed table (fluke_fp8_prepare_weight does that step ahead of time,
+ * fluke_fp8_release_weight drops it). The *_plain_gpu variants take row-major weights and
  * allocate nothing. */
 #include <fluke/fluke.h>
 
@@ -16,9 +17,6 @@
 #include "gpu_common.h"
 
 int fluke_dims_supported(fluke_dims_t d); /* fused_i8.c */
-
-/* device allocation helpers implemented next to the kernels */
-
 
 struct fluke_fp8_backend {
     fluke_dims_t dims;
@@ -56,27 +54,89 @@ fluke_fp8_backend_t *fluke_fp8_select(int device_index, fluke_dims_t dims) {
 }
 
 /* ---- re-ordered weight cache -------------------------------------------------------------- */
+/* Keyed by (device, pointer, N, K). The library cannot see a caller free or overwrite a weight, so
+ * the contract is pointer identity: a caller that re-uses a weight address for other contents
+ * calls fluke_fp8_release_weight first. The table is guarded by a mutex; when it is full the
+ * oldest entry is dropped (its copy is freed after the device has finished with it; a process
+ * that keeps more than 64 fp8 weights live and calls from several threads should use the
+ * *_plain_gpu entry points, since a copy handed to one thread's call can then be dropped by
+ * another thread's). */
+
+#include <pthread.h>
 
 #define FLUKE_FP8_CACHE_SLOTS 64
-static struct { const void *src; int N, K; void *plain; } g_wcache[FLUKE_FP8_CACHE_SLOTS];
-static int g_wcache_used = 0;
+static struct { const void *src; int dev, N, K; void *plain; unsigned long age; } g_wcache[FLUKE_FP8_CACHE_SLOTS];
+static unsigned long g_wcache_clock = 0;
+static pthread_mutex_t g_wcache_lock = PTHREAD_MUTEX_INITIALIZER;
+
+/* Hooks the CPU tests replace to exercise the table without a GPU. */
+static int (*g_hook_malloc)(void **, size_t) = fluke_sm100_malloc;
+static int (*g_hook_free)(void *) = fluke_sm100_free;
+static int (*g_hook_unshuffle)(void *, const void *, int, int, void *) = fluke_sm100_fp8_unshuffle;
+static int (*g_hook_device)(void) = fluke_sm100_current_device;
+void fluke_fp8_cache_test_hooks(int (*m)(void **, size_t), int (*f)(void *),
+                                int (*u)(void *, const void *, int, int, void *), int (*d)(void)) {
+    g_hook_malloc = m ? m : fluke_sm100_malloc;
+    g_hook_free = f ? f : fluke_sm100_free;
+    g_hook_unshuffle = u ? u : fluke_sm100_fp8_unshuffle;
+    g_hook_device = d ? d : fluke_sm100_current_device;
+}
 
 static const void *plain_weight(const void *preshuffled, int N, int K) {
-    int i;
+    int i, slot = -1, dev;
     void *dst = NULL;
-    for (i = 0; i < g_wcache_used; ++i)
-        if (g_wcache[i].src == preshuffled && g_wcache[i].N == N && g_wcache[i].K == K)
-            return g_wcache[i].plain;
-    if (g_wcache_used == FLUKE_FP8_CACHE_SLOTS) return NULL;
-    if (fluke_host_note_error(fluke_sm100_malloc(&dst, (size_t)N * K)) != 0) return NULL;
-    if (fluke_host_note_error(fluke_sm100_fp8_unshuffle(dst, preshuffled, N, K, fluke_host_stream())) != 0)
-        return NULL;
-    g_wcache[g_wcache_used].src = preshuffled;
-    g_wcache[g_wcache_used].N = N;
-    g_wcache[g_wcache_used].K = K;
-    g_wcache[g_wcache_used].plain = dst;
-    ++g_wcache_used;
-    return dst;
+    const void *found = NULL;
+    if (!preshuffled) return NULL;
+    dev = g_hook_device();
+    pthread_mutex_lock(&g_wcache_lock);
+    for (i = 0; i < FLUKE_FP8_CACHE_SLOTS; ++i)
+        if (g_wcache[i].plain && g_wcache[i].src == preshuffled && g_wcache[i].dev == dev &&
+            g_wcache[i].N == N && g_wcache[i].K == K) {
+            found = g_wcache[i].plain;
+            break;
+        }
+    if (!found) {
+        /* a free slot, else the oldest entry */
+        for (i = 0; i < FLUKE_FP8_CACHE_SLOTS; ++i) {
+            if (!g_wcache[i].plain) { slot = i; break; }
+            if (slot < 0 || g_wcache[i].age < g_wcache[slot].age) slot = i;
+        }
+        if (fluke_host_note_error(g_hook_malloc(&dst, (size_t)N * K)) == 0) {
+            if (fluke_host_note_error(g_hook_unshuffle(dst, preshuffled, N, K, fluke_host_stream())) == 0) {
+                if (g_wcache[slot].plain) g_hook_free(g_wcache[slot].plain);
+                g_wcache[slot].src = preshuffled;
+                g_wcache[slot].dev = dev;
+                g_wcache[slot].N = N;
+                g_wcache[slot].K = K;
+                g_wcache[slot].plain = dst;
+                g_wcache[slot].age = ++g_wcache_clock;
+                found = dst;
+            } else {
+                g_hook_free(dst);
+            }
+        }
+    }
+    pthread_mutex_unlock(&g_wcache_lock);
+    return found;
+}
+
+int fluke_fp8_prepare_weight(const void *preshuffled, int N, int K) {
+    if (N <= 0 || K <= 0 || N % 16 || K % 16) return -1;
+    return plain_weight(preshuffled, N, K) ? 0 : -1;
+}
+
+int fluke_fp8_release_weight(const void *preshuffled) {
+    int i, n = 0;
+    pthread_mutex_lock(&g_wcache_lock);
+    for (i = 0; i < FLUKE_FP8_CACHE_SLOTS; ++i)
+        if (g_wcache[i].plain && (!preshuffled || g_wcache[i].src == preshuffled)) {
+            g_hook_free(g_wcache[i].plain);
+            g_wcache[i].plain = NULL;
+            g_wcache[i].src = NULL;
+            ++n;
+        }
+    pthread_mutex_unlock(&g_wcache_lock);
+    return n;
 }
 
 int fluke_fp8_unshuffle_gpu(void *dst_nk, const void *src_preshuffled, int N, int K) {

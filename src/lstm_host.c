@@ -46,6 +46,9 @@ int fluke_factored_lstm_layer_i8_gpu(const fluke_flstm_layer_t *layer) {
     return fluke_host_note_error(fluke_sm100_lstm_layer(layer, fluke_host_stream()));
 }
 
+/* Measurement aid of the benchmark, not part of the public header: launches only some kernel
+ * classes of the layer (1 = x_down GEMM, 2 = per-step down-projection, 4 = per-step fused step). */
+int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int phase_mask);
 int fluke_factored_lstm_layer_phases_gpu(const fluke_flstm_layer_t *layer, int phase_mask) {
     if (!layer) return -1;
     return fluke_host_note_error(fluke_sm100_lstm_layer_phases(layer, phase_mask, fluke_host_stream()));

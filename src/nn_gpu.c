@@ -6,8 +6,10 @@
 #include "error.h"
 #include "gpu_common.h"
 
-static void *g_stream = NULL;
-static int g_last_error = 0;
+/* Per host thread: a process that drives several GPUs from one thread each gives every thread
+ * its own stream (and reads back its own last error) without racing on shared state. */
+static _Thread_local void *g_stream = NULL;
+static _Thread_local int g_last_error = 0;
 
 void fluke_set_stream(void *cuda_stream) { g_stream = cuda_stream; }
 void *fluke_get_stream(void) { return g_stream; }

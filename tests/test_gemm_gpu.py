@@ -35,6 +35,16 @@ def be8():
     return b
 
 
+@pytest.fixture(autouse=True)
+def _fp8_weight_copies_dropped(flib):
+    """The reference-ABI fp8 entry points find their re-ordered copy of a weight by the weight's
+    ADDRESS; these tests create and free weights all the time and torch hands the same addresses
+    out again, so every test ends by dropping the copies, as the contract asks of a caller that
+    frees a weight."""
+    yield
+    flib.fluke_fp8_release_weight(None)
+
+
 def test_select_rejects_other_dims_and_reports_dims(flib, be):
     assert flib.fluke_int8_select(0, L.fluke_dims_t(768, 2048, 8, 64, 2048)) is None
     assert flib.fluke_fp8_select(0, L.fluke_dims_t(512, 2048, 16, 64, 2048)) is None
@@ -194,13 +204,44 @@ def test_gated_mlp_against_silu_mul_kernel_and_full_size(be):
     assert (out.float() - two.float()).abs().max() < 0.05
 
 
-def test_gated_mlp_golden_from_reference_test(golden_tests):
-    """N = 256 in the fixture, so this goes through the oracle epilogue on GPU accumulators."""
+def _sample_rows(m, seqlen, seed):
+    """First and last tiles, the rows around a sequence boundary and a 128-row tile edge, 256 random rows."""
+    return torch.cat([torch.arange(0, 64), torch.arange(seqlen - 1, seqlen + 63), torch.arange(128 * 100 - 8, 128 * 100 + 8),
+                      torch.randint(0, m, (256,), generator=torch.Generator().manual_seed(seed)), torch.arange(m - 64, m)])
+
+
+def test_gated_mlp_full_size_sampled_rows_vs_oracle(be):
+    """M = 32000 (the benchmark shape) through the fused kernel, sampled rows against the oracle
+    (reference: cute/test_dual_gemm_silu.py:90-96)."""
+    m = 32000
+    g = torch.Generator().manual_seed(40)
+    a, sa = prep.quantize_int8_rows(torch.randn(m, 512, generator=g))
+    wg, sg = prep.quantize_int8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    wu, su = prep.quantize_int8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    out = ops.gated_mlp_i8(be, a.to(DEV), wg.to(DEV), wu.to(DEV), sa.to(DEV), sg.to(DEV), su.to(DEV))
+    rows = _sample_rows(m, 1000, 6)
+    exp = port.gated_mlp_i8(a[rows].numpy(), wg.numpy(), wu.numpy(), sa[rows].numpy(), sg.numpy(), su.numpy()).astype(np.float32)
+    got = out[rows.to(DEV)].float().cpu().numpy()
+    assert np.abs(got - exp).max() <= TOL_REL_RMS * np.sqrt((exp ** 2).mean())
+
+
+def test_gated_mlp_golden_from_reference_test(be, golden_tests):
+    """The fixture of the reference's own test (cute/test_dual_gemm_silu.py, N cut to 256) through
+    the FUSED kernel: its 256 gate/up rows are the first rows of 2048-row weights padded with zero
+    rows (output columns are independent), so columns [0, 256) must meet the test's 0.05."""
     g = golden_tests
-    T = lambda k: torch.from_numpy(g[k]).to(DEV)
-    acc_g, acc_u = ops.gemm_i8_s32(T("silu_A"), T("silu_Bg")).cpu().numpy(), ops.gemm_i8_s32(T("silu_A"), T("silu_Bu")).cpu().numpy()
-    got = port.epi_silu(acc_g, acc_u, g["silu_sa"], g["silu_sbg"], g["silu_sbu"])
-    assert np.abs(got.astype(np.float32) - g["silu_expected"].astype(np.float32)).max() < 0.05
+    pad = lambda w: np.concatenate([w, np.zeros((2048 - w.shape[0],) + w.shape[1:], w.dtype)], 0)
+    T = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    got = ops.gated_mlp_i8(be, T(g["silu_A"]), T(pad(g["silu_Bg"])), T(pad(g["silu_Bu"])), T(g["silu_sa"]),
+                           T(pad(g["silu_sbg"])), T(pad(g["silu_sbu"])))
+    got = got.float().cpu().numpy()
+    assert np.abs(got[:, :256] - g["silu_expected"].astype(np.float32)).max() < 0.05  # ABS_TOL of the reference test
+    assert not got[:, 256:].any()
+    # and the oracle's epilogue on the same accumulators, against the same fixture
+    acc_g, acc_u = ops.gemm_i8_s32(T(g["silu_A"]), T(g["silu_Bg"])).cpu().numpy(), ops.gemm_i8_s32(T(g["silu_A"]), T(g["silu_Bu"])).cpu().numpy()
+    ora = port.epi_silu(acc_g, acc_u, g["silu_sa"], g["silu_sbg"], g["silu_sbu"]).astype(np.float32)
+    assert np.abs(ora - g["silu_expected"].astype(np.float32)).max() < 0.05
+    assert np.abs(got[:, :256] - ora).max() <= TOL_REL_RMS * np.sqrt((ora ** 2).mean())
 
 
 # ---- fp8 (E4M3, amax/448) ---------------------------------------------------------------------------------
@@ -234,6 +275,58 @@ def test_fp8_unshuffle_and_fused_ops(be8, golden_tests):
     w_nk = torch.from_numpy(np.ascontiguousarray(gt["fp8_B_kn"].T))
     got = ops.qkv_rotary_fp8(be8, T("fp8_A"), prep.preshuffle_fp8_weight(w_nk).to(DEV), T("fp8_sa"), T("fp8_sb"), T("fp8_sin"), T("fp8_cos"), 16)
     assert (got.float().cpu() - torch.from_numpy(gt["fp8_rot_expected"].astype(np.float32))).abs().max() < 5e-2
+
+
+def test_fp8_fused_ops_full_size_sampled_rows(be8):
+    """M = 32000, seqlen 1000 (the benchmark shape: the sequence-aligned tiling of the rotary
+    epilogue) for both fused fp8 entry points, sampled rows against the oracle; tolerance of the
+    reference's fp8 tests (fly/test_rotary.py:103: 5e-2) and 1e-2 of the output RMS."""
+    m, seqlen = 32000, 1000
+    g = torch.Generator().manual_seed(41)
+    a, sa = prep.quantize_fp8_rows(torch.randn(m, 512, generator=g))
+    w, sb = prep.quantize_fp8_rows(torch.randn(1536, 512, generator=g) * 0.02)
+    sin, cos = prep.rotary_tables(seqlen, 64)
+    a8, w8 = a.view(torch.uint8), w.view(torch.uint8)
+    A, SA = a8.to(DEV), sa.to(DEV)
+    rows = _sample_rows(m, seqlen, 8)
+    pos = rows % seqlen
+    out = ops.qkv_rotary_fp8(be8, A, prep.preshuffle_fp8_weight(w).to(DEV), SA, sb.to(DEV), sin.to(DEV), cos.to(DEV), seqlen)
+    exp = port.epi_rotary(port.gemm_fp8_f32(a8[rows].numpy(), w8.numpy()), sa[rows].numpy(), sb.numpy(),
+                          sin[pos].numpy(), cos[pos].numpy(), len(rows), 1024).astype(np.float32)
+    err = np.abs(out[rows.to(DEV)].float().cpu().numpy() - exp).max()
+    assert err <= TOL_REL_RMS * np.sqrt((exp ** 2).mean()) and err < 5e-2
+    wg, sg = prep.quantize_fp8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    wu, su = prep.quantize_fp8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    out = ops.gated_mlp_fp8(be8, A, prep.preshuffle_fp8_weight(wg).to(DEV), prep.preshuffle_fp8_weight(wu).to(DEV),
+                            SA, sg.to(DEV), su.to(DEV))
+    exp = port.epi_silu(port.gemm_fp8_f32(a8[rows].numpy(), wg.view(torch.uint8).numpy()),
+                        port.gemm_fp8_f32(a8[rows].numpy(), wu.view(torch.uint8).numpy()),
+                        sa[rows].numpy(), sg.numpy(), su.numpy()).astype(np.float32)
+    err = np.abs(out[rows.to(DEV)].float().cpu().numpy() - exp).max()
+    assert err <= TOL_REL_RMS * np.sqrt((exp ** 2).mean()) and err < 5e-2
+
+
+def test_fp8_weight_copy_follows_the_address_until_released(be8, flib):
+    """New weight bytes written to an address the library has seen: the kept copy (the old weight)
+    is used until fluke_fp8_release_weight is called for that address, the new one afterwards."""
+    g = torch.Generator().manual_seed(14)
+    m = 256
+    a, sa = prep.quantize_fp8_rows(torch.randn(m, 512, generator=g))
+    w1, s1 = prep.quantize_fp8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    w2, _ = prep.quantize_fp8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    up, su = prep.quantize_fp8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    A, SA, S1, SU = a.view(torch.uint8).to(DEV), sa.to(DEV), s1.to(DEV), su.to(DEV)
+    UP = prep.preshuffle_fp8_weight(up).to(DEV)
+    gate = prep.preshuffle_fp8_weight(w1).to(DEV)
+    run = lambda: ops.gated_mlp_fp8(be8, A, gate, UP, SA, S1, SU).clone()
+    first = run()
+    gate.copy_(prep.preshuffle_fp8_weight(w2).to(DEV))     # same address, other contents
+    assert torch.equal(run(), first)                        # the kept copy still answers
+    assert flib.fluke_fp8_release_weight(gate.data_ptr()) == 1
+    second = run()
+    want = ops.gated_mlp_fp8(be8, A, w2.view(torch.uint8).to(DEV), up.view(torch.uint8).to(DEV), SA, S1, SU, plain=True)
+    assert torch.equal(second, want) and not torch.equal(second, first)
+    assert flib.fluke_fp8_prepare_weight(gate.data_ptr(), 2048, 512) == 0    # already there: nothing to do
 
 
 def test_fp8_base_gemm_vs_oracle():

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from fluke_b200 import lib as L, ops, prep
-from fluke_b200.lstm import FactoredLstmLayer, StackPipeline, run_stack
+from fluke_b200.lstm import FactoredLstmLayer, StackPipeline, run_stack, run_stack_c
 from fluke_b200.shard import shard_range
 from oracle import port
 
@@ -18,15 +18,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-LSTM_MODES = {"cluster": 1, "persistent_l2": 2, "per_step": 0}
+# name -> (mode for fluke_set_lstm_persistent, form fluke_sm100_lstm_last_form then reports)
+LSTM_MODES = {"cluster": (4, 1), "persistent_l2": (2, 2), "per_step": (0, 0)}
 
 
 @pytest.fixture(params=list(LSTM_MODES))
 def lstm_mode(request, flib):
     """Runs a test with each form of the layer recurrence: one launch with the exchange inside
-    thread-block clusters (the default where the shape allows it), one launch with the exchange
-    through L2, and two launches per step."""
-    flib.fluke_set_lstm_persistent(LSTM_MODES[request.param])
+    thread-block clusters, one launch with the exchange through L2, and two launches per step."""
+    flib.fluke_set_lstm_persistent(LSTM_MODES[request.param][0])
     yield request.param
     flib.fluke_set_lstm_persistent(1)
 
@@ -97,7 +97,7 @@ def test_layer_vs_oracle(T, B, reverse, lstm_mode):
     c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
     ho = ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale,
                                     layer.w_up, layer.bias, c, h, reverse=reverse)
-    assert L.load().fluke_sm100_lstm_last_form() == LSTM_MODES[lstm_mode]  # each form covers this shape
+    assert L.load().fluke_sm100_lstm_last_form() == LSTM_MODES[lstm_mode][1]  # each form covers this shape
     he, ce, hf = _run_oracle_layer(layer, x, xs, reverse)
     d = np.abs(ho.cpu().numpy().astype(np.int32) - he.astype(np.int32))
     assert d.max() <= 1 and (d != 0).mean() < 5e-3
@@ -148,6 +148,24 @@ def test_stack_alternating_directions_and_batch_shards(lstm_mode):
     assert d.max() <= 2 and (d > 1).mean() < 1e-3 and (d != 0).mean() < 2e-2
 
 
+def test_stack_entry_point_equals_layer_by_layer(flib):
+    """fluke_factored_lstm_stack_i8_gpu (one C call per pass) gives the bytes and the final state
+    of the layer-by-layer loop; 4 layers (even count: the first layer writes the scratch buffer)
+    and a single layer (no scratch buffer needed)."""
+    T, B, H, R = 6, 200, 768, 128
+    g = torch.Generator().manual_seed(5)
+    x, xs = prep.quantize_int8_rows(torch.randn(T * B, H, generator=g))
+    X, XS = x.view(T, B, H).to(DEV), xs.to(DEV)
+    for n_layers in (4, 1, 3):
+        layers = [FactoredLstmLayer.random(H, R, bool(i % 2), g, DEV) for i in range(n_layers)]
+        want, state = run_stack(layers, X, XS)
+        got, (c, h) = run_stack_c(layers, X, XS)
+        assert torch.equal(got, want)
+        for i in range(n_layers):
+            assert torch.equal(c[i], state[i][0]) and torch.equal(h[i], state[i][1])
+    assert flib.fluke_factored_lstm_stack_i8_gpu(None, 0, T, B, H, R, 0, 0, 0, 0, 0, 0, 0, 0) != 0  # bad arguments: refused
+
+
 def test_persistent_and_per_step_layers_agree(flib):
     """Same layer through all three drivers: the only difference is the accumulation order of the two
     K halves, so codes differ by at most one, rarely. Also other hidden sizes (1024, 384 with an odd
@@ -156,7 +174,7 @@ def test_persistent_and_per_step_layers_agree(flib):
     for (T, B, H) in [(16, 300, 768), (6, 130, 1024), (5, 1024, 768), (4, 140, 384), (4, 70, 512), (3, 1100, 768)]:
         layer, x, xs = _layer_case(T, B, H, 128, 11 + B, False)
         outs = []
-        for mode in (1, 2, 0):
+        for mode in (4, 2, 0):
             flib.fluke_set_lstm_persistent(mode)
             c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
             outs.append((ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh,
@@ -178,9 +196,10 @@ def test_cluster_form_runs_in_rounds_when_nothing_else_covers_the_shape(flib):
     T, B, H, R = 4, 2100, 192, 128
     layer, x, xs = _layer_case(T, B, H, R, 5, True)
     c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
-    flib.fluke_set_lstm_persistent(1)
+    flib.fluke_set_lstm_persistent(4)
     ho = ops.factored_lstm_layer_i8(x.to(DEV), xs.to(DEV), layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale,
                                     layer.w_up, layer.bias, c, h, reverse=True)
+    flib.fluke_set_lstm_persistent(1)
     assert flib.fluke_sm100_lstm_last_form() == 1
     he, ce, _ = _run_oracle_layer(layer, x, xs, True)
     d = np.abs(ho.cpu().numpy().astype(np.int32) - he.astype(np.int32))
@@ -198,9 +217,8 @@ def test_layer_config_size_properties(lstm_mode):
     args = (layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale, layer.w_up, layer.bias)
     c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
     fwd = ops.factored_lstm_layer_i8(X, XS, *args, c, h, reverse=False).clone()
-    # 8 row tiles are more than the clusters a B200 holds at once (7), so mode 1 picks the L2 form
     form = L.load().fluke_sm100_lstm_last_form()
-    assert form == (2 if lstm_mode == "cluster" else LSTM_MODES[lstm_mode])
+    assert form == LSTM_MODES[lstm_mode][1]
     assert int(fwd.min()) >= -127
     c2 = torch.zeros(B, H, device=DEV); h2 = torch.zeros(B, H, dtype=torch.int8, device=DEV)
     rev = ops.factored_lstm_layer_i8(X.flip(0).contiguous(), XS.view(T, B).flip(0).contiguous().view(-1), *args, c2, h2, reverse=True)
