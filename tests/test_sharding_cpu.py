@@ -49,3 +49,19 @@ def test_gloo_world2_timing_reduction():
     ms, tot = q.get(timeout=120)
     [p.join(60) for p in procs]
     assert ms == 15.0 and tot == 2 * 1024 * 1000 * 5
+
+
+def test_strong_scaling_record_and_roofline_fractions():
+    """The strong-scaling sub-record of the bench line (1024 chunks in total over the ranks) and
+    the fractions quoted for the GEMM entries."""
+    from bench import roofline_fractions, strong_scaling_record
+    r = strong_scaling_record(1024, 8, 10.0)
+    assert r["chunks_per_gpu"] == 128 and r["chunks_total"] == 1024
+    assert r["value"] == 1024 * 1000 * 5 / 10e-3
+    assert strong_scaling_record(1024, 3, 10.0)["chunks_per_gpu"] == 342   # the largest shard sets the time
+    # 134.22 GOP and 149.7 MB in 50 us against 4500 TOP/s and 6538.6 GB/s: tensor floor 29.8 us, HBM floor 22.9 us
+    ft, fh, ff = roofline_fractions(50.0, 134.22e9, 149.7e6, 4500.0, 6538.6)
+    assert abs(ft - 0.597) < 2e-3 and abs(fh - 0.458) < 2e-3 and ff == ft
+    ft, fh, ff = roofline_fractions(30.0, 50.33e9, 115.87e6, 4500.0, 6538.6)      # HBM-bound shape
+    assert ff == fh and ft < fh
+    assert roofline_fractions(10.0, 0.0, 65.79e6, None, 6538.6)[0] is None
