@@ -48,13 +48,20 @@ SM100_SRC = fluke_b200/csrc/fluke_sm100_all.cu
 SM100_DEPS = $(wildcard fluke_b200/csrc/*.cu fluke_b200/csrc/*.cuh fluke_b200/csrc/*.h)
 
 PROBELIB = $(BUILD_DIR)/libfluke_probe.so
+WAITPROBELIB = $(BUILD_DIR)/libfluke_waitprobe.so
 
-.PHONY: all shared probe clean distclean
+.PHONY: all shared probe waitprobe clean distclean
 
 all: $(STATICLIB)
 shared: $(SHAREDLIB)
 # tcgen05 issue-rate probe the benchmark compares the GEMM kernels with; not part of libfluke
 probe: $(PROBELIB)
+
+# test-only kernels that make the bounded device waits run out (tests/test_wait_timeout_gpu.py)
+waitprobe: $(WAITPROBELIB)
+
+$(WAITPROBELIB): tests/csrc/wait_probe.cu $(SM100_DEPS) | $(BUILD_DIR)
+	$(NVCC) $(CUDA_CFLAGS) $(CPPFLAGS) -shared tests/csrc/wait_probe.cu -o $@ $(CUDA_LDFLAGS)
 
 $(PROBELIB): fluke_b200/csrc/mma_peak_sm100.cu $(SM100_DEPS) | $(BUILD_DIR)
 	$(NVCC) $(CUDA_CFLAGS) $(CPPFLAGS) -shared fluke_b200/csrc/mma_peak_sm100.cu -o $@ $(CUDA_LDFLAGS)

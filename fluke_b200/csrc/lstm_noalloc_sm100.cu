@@ -1,10 +1,9 @@
 // lstm_noalloc_sm100.cu -- a factored-LSTM layer entry point for callers that cannot allocate
 // device memory.
 //
-// Some hosts of this library may not call cudaMalloc at the point where they run a layer: code
-// inside a CUDA-graph capture or another region where allocation is forbidden, plug-ins that
-// are handed device pointers but own no allocator, and services whose memory budget is fixed
-// at start-up. fluke_factored_lstm_layer_i8_gpu asks such a caller for a workspace it has no
+// Some hosts of this library may not call cudaMalloc at the point where they run a layer:
+// plug-ins that are handed device pointers but own no allocator, services whose memory budget
+// is fixed at start-up, and code in regions where the CUDA allocator must not be called. fluke_factored_lstm_layer_i8_gpu asks such a caller for a workspace it has no
 // way to provide. The variant below takes the same layer description, ignores its workspace
 // fields and keeps the intermediate tensors (hh_down [B,R] and x_down [T,B,R], f16) in a fixed
 // 4 MiB array that is part of the library image, so nothing is allocated -- by this function or
@@ -13,14 +12,18 @@
 // What to know before using it:
 //  * Size limit. The layer must fit the built-in array:
 //    fluke_factored_lstm_layer_workspace(T,B,H,R) <= FLUKE_LSTM_NOALLOC_SCRATCH_BYTES (4 MiB),
-//    e.g. 1024 chunks x 15 timesteps at rank 128. Larger layers are refused with a message on
+//    e.g. 1024 chunks x 14 timesteps, or 128 chunks x 126 timesteps, at rank 128 (the workspace
+//    is 256 bytes x (T + 1) per chunk plus 1 KB). Larger layers are refused with a message on
 //    stderr and a non-zero return; nothing is launched. Long sequences can be run as several
 //    calls, the state (c, h) carries over.
 //  * Cost. Every GPU on which the library is loaded holds the 4 MiB until the process exits,
 //    whether or not this entry point is ever called.
 //  * First call per device. It looks up the device address of the array (the array's name in
 //    host code is only a host-side handle, not something a kernel can dereference) and caches
-//    it. Make that first call outside any stream capture, with the device current.
+//    it, and the kernels it launches are configured on their first use. Make the first call on
+//    a device -- with the layer shape (B, H, R) and the fluke_set_lstm_persistent mode that later
+//    calls will use, since those choose the kernels -- before any stream capture begins, with the
+//    device current.
 //  * One layer at a time per device. All calls share the one array; it still holds the previous
 //    call's intermediates when the next call starts. That is harmless -- every element a layer
 //    reads has been written by the same call first, and rows past B are never read from memory

@@ -114,43 +114,6 @@ struct PersistSmem {
     static_assert(kDynamic <= 232448, "shared memory budget of one CTA exceeded");
 };
 
-__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned int ld_relaxed_u32(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// Waits until *flag >= target. Gives up when the cycle limit passes or another CTA has raised
-// the global abort word; then raises both abort flags and returns false.
-__device__ __forceinline__ bool wait_counter(const unsigned int *flag, unsigned int target,
-                                             unsigned int *g_abort, volatile int *abort_flag,
-                                             unsigned int site) {
-    const long long t0 = clock64();
-    unsigned int spins = 0;
-    for (;;) {
-        // poll with relaxed loads; one acquire fence orders the data reads after the sighting
-        if (ld_relaxed_u32(flag) >= target) {
-            asm volatile("fence.acq_rel.gpu;" ::: "memory");
-            return true;
-        }
-        if (*abort_flag) return false;
-        if ((++spins & 63u) == 0u) {
-            const bool late = clock64() - t0 > kWaitCycleLimit;
-            if (late || ld_acquire_u32(g_abort) != 0u) {
-                if (late) report_timeout(site);
-                *abort_flag = 1;
-                atomicExch(g_abort, 1u);
-                return false;
-            }
-        }
-    }
-}
-
 // Barrier over a set of warps built on an mbarrier so that, unlike bar.sync, the wait is
 // bounded: one arrival per warp (release at CTA scope), then every thread waits for the phase.
 __device__ __forceinline__ bool warps_barrier(uint64_t *bar, uint32_t parity, int lane,

@@ -102,11 +102,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return done != 0;
 }
 
-// Waits for the phase with the given parity to complete. Gives up after kWaitCycleLimit
-// cycles: records `site` in the status word, raises *abort_flag (shared memory, seen by the
-// other roles of the CTA) and returns false. A raised abort flag also ends the wait.
+// Waits for the phase with the given parity to complete. Gives up after `limit` cycles
+// (kWaitCycleLimit in every kernel of the library): records `site` in the status word, raises
+// *abort_flag (shared memory, seen by the other roles of the CTA) and returns false. A raised
+// abort flag also ends the wait.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned int site) {
+                                          unsigned int site, long long limit = kWaitCycleLimit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -114,10 +115,51 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycleLimit) {
+        if (clock64() - t0 > limit) {
             report_timeout(site);
             *abort_flag = 1;
             return false;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Counters in global memory that CTAs of one launch hand data over with
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned int ld_relaxed_u32(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Waits until *flag >= target. Gives up when `limit` cycles have passed or another CTA has raised
+// the global abort word; then raises both abort flags and returns false (a timeout also records
+// `site` in the status word).
+__device__ __forceinline__ bool wait_counter(const unsigned int *flag, unsigned int target,
+                                             unsigned int *g_abort, volatile int *abort_flag,
+                                             unsigned int site, long long limit = kWaitCycleLimit) {
+    const long long t0 = clock64();
+    unsigned int spins = 0;
+    for (;;) {
+        // poll with relaxed loads; one acquire fence orders the data reads after the sighting
+        if (ld_relaxed_u32(flag) >= target) {
+            asm volatile("fence.acq_rel.gpu;" ::: "memory");
+            return true;
+        }
+        if (*abort_flag) return false;
+        if ((++spins & 63u) == 0u) {
+            const bool late = clock64() - t0 > limit;
+            if (late || ld_acquire_u32(g_abort) != 0u) {
+                if (late) report_timeout(site);
+                *abort_flag = 1;
+                atomicExch(g_abort, 1u);
+                return false;
+            }
         }
     }
 }

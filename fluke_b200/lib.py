@@ -77,6 +77,8 @@ SIGNATURES = {
     "fluke_gated_mlp_fp8_plain_gpu": (I, [P, P, P, P, P, P, P, P, I]),
     "fluke_down_proj_i8_gpu": (I, [P, I, P, P, P, P, I, I, I]),
     "fluke_factored_lstm_step_i8_gpu": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I]),
+    "fluke_down_proj_fp8_gpu": (I, [P, I, P, P, P, P, I, I, I]),
+    "fluke_factored_lstm_step_fp8_gpu": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I]),
     "fluke_factored_lstm_layer_workspace": (Z, [I, I, I, I]),
     "fluke_factored_lstm_layer_i8_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t)]),
     "fluke_factored_lstm_layer_phases_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t), I]),
@@ -104,8 +106,9 @@ PROBE_PATH = os.path.join(ROOT, "lib", "libfluke_probe.so")
 
 
 def build(verbose=False):
-    """`make shared probe cuda=1` at the repository root (nvcc cross-compiles sm_100a without a GPU)."""
-    cmd = ["make", "shared", "probe", "cuda=1"]
+    """`make shared probe waitprobe cuda=1` at the repository root (nvcc cross-compiles sm_100a
+    without a GPU): the library, the benchmark's issue-rate probe and the tests' wait probe."""
+    cmd = ["make", "shared", "probe", "waitprobe", "cuda=1"]
     res = subprocess.run(cmd, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if verbose or res.returncode != 0:
         print(res.stdout)

@@ -231,7 +231,18 @@ def down_proj_i8(a_i8, w_i8, scale_a, scale_b, out=None):
     return out
 
 
-def factored_lstm_step_i8(A, W4, bias4, c, h_out=None):
+def down_proj_fp8(a_fp8, w_fp8_nk, scale_a, scale_b, out=None):
+    """f16 [M,N] = (e4m3 GEMM * sa[m]) * sb[n]; a_fp8 [M,K], w_fp8_nk [N,K] as uint8 e4m3 bytes."""
+    _dev(a_fp8, w_fp8_nk, scale_a, scale_b)
+    m, k = a_fp8.shape
+    n = w_fp8_nk.size(0)
+    out = torch.empty(m, n, dtype=torch.float16, device=a_fp8.device) if out is None else out
+    _check(_L().fluke_down_proj_fp8_gpu(_p(out), out.stride(0), _p(a_fp8), _p(w_fp8_nk), _p(scale_a), _p(scale_b),
+                                        m, n, k), "fluke_down_proj_fp8_gpu")
+    return out
+
+
+def factored_lstm_step_i8(A, W4, bias4, c, h_out=None, fp8_export_name=False):
     """A f16 [B,Kc]; W4 f16 [4H,Kc] (gate-major i,f,g,o); bias4 f32 [4H]; c f32 [B,H] in place."""
     _dev(A, W4, bias4, c)
     b, kc = A.shape
@@ -239,8 +250,9 @@ def factored_lstm_step_i8(A, W4, bias4, c, h_out=None):
     h_out = torch.empty(b, h, dtype=torch.int8, device=A.device) if h_out is None else h_out
     w = [W4.data_ptr() + g * h * kc * 2 for g in range(4)]
     bs = [bias4.data_ptr() + g * h * 4 for g in range(4)]
-    _check(_L().fluke_factored_lstm_step_i8_gpu(_p(A), w[0], w[1], w[2], w[3], bs[0], bs[1], bs[2], bs[3],
-                                                _p(c), _p(h_out), b, h, kc), "fluke_factored_lstm_step_i8_gpu")
+    fn = _L().fluke_factored_lstm_step_fp8_gpu if fp8_export_name else _L().fluke_factored_lstm_step_i8_gpu
+    _check(fn(_p(A), w[0], w[1], w[2], w[3], bs[0], bs[1], bs[2], bs[3], _p(c), _p(h_out), b, h, kc),
+           "fluke_factored_lstm_step_i8_gpu")
     return h_out
 
 

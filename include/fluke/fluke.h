@@ -367,6 +367,33 @@ int fluke_factored_lstm_step_i8_gpu(
     int B, int H, int Kc
 );
 
+/* The two kernels of the reference's fp8 factored-LSTM export
+ * (fly/rdna4/factored_lstm/export_fp8_factored_lstm.py).
+ *   fluke_down_proj_fp8_gpu          its down-projection (:161-181, `down_proj_fp8_R{R}_K{H}`): the fp8
+ *                                    base GEMM with N = R, K = H: out f16 [M,N] (row stride ld_out) =
+ *                                    f16((f32(a @ w^T) * scale_a[m]) * scale_b[n]), a e4m3 [M,K] with
+ *                                    per-row scales, w e4m3 [N,K] ROW-MAJOR with per-channel scales
+ *                                    (a PRESHUFFLED weight goes through fluke_fp8_unshuffle_gpu once).
+ *                                    K % 16 == 0, K <= 1024, N % 64 == 0.
+ *   fluke_factored_lstm_step_fp8_gpu its fused step (rdna_fp8_factored_lstm.py:113-294). In that export
+ *                                    only the down-projection is fp8: the step contracts f16
+ *                                    [hh_down | x_down] with f16 up-projections and writes int8 h at
+ *                                    1/127, i.e. it IS fluke_factored_lstm_step_i8_gpu; the name exists so
+ *                                    that a caller of the fp8 export finds its two symbols.
+ * How h (int8 at 1/127) becomes the e4m3 operand of the next down-projection is the caller's
+ * step (slorado; not part of the reference checkout). */
+int fluke_down_proj_fp8_gpu(
+    void *out_f16, int ld_out, const void *a_fp8, const void *w_fp8_nk,
+    const void *scale_a, const void *scale_b, int M, int N, int K
+);
+int fluke_factored_lstm_step_fp8_gpu(
+    const void *A,
+    const void *W_i, const void *W_f, const void *W_g, const void *W_o,
+    const void *bias_i, const void *bias_f, const void *bias_g, const void *bias_o,
+    void *c, void *h_out,
+    int B, int H, int Kc
+);
+
 /* One whole factored-LSTM layer over T timesteps (the loop slorado's CRFModel drives,
  * README.md:82-92): x_down = down_proj(x, dn_ih) for all t, then per step
  * hh_down = down_proj(h_{t-1}, dn_hh), gates on [hh_down | x_down_t], cell update,
@@ -460,13 +487,15 @@ int  fluke_flstm_stream_drain(fluke_flstm_stream_t *s);
 void fluke_flstm_stream_destroy(fluke_flstm_stream_t *s);
 
 /* No counterpart in the reference. The same layer as fluke_factored_lstm_layer_i8_gpu for
- * callers that cannot allocate device memory (inside a stream capture, plug-ins without an
- * allocator, fixed memory budgets): layer->workspace / workspace_bytes are ignored and the
+ * callers that cannot allocate device memory (plug-ins without an allocator, fixed memory
+ * budgets, regions where the CUDA allocator must not be called): layer->workspace /
+ * workspace_bytes are ignored and the
  * intermediates live in a FLUKE_LSTM_NOALLOC_SCRATCH_BYTES array built into the library, held
  * by every GPU that loads it. Nothing is allocated. The layer must satisfy
  * fluke_factored_lstm_layer_workspace(T,B,H,R) <= FLUKE_LSTM_NOALLOC_SCRATCH_BYTES, otherwise
- * a message is printed and non-zero returned. The first call on a device resolves the array's
- * device address: make it outside any stream capture. All calls share the array, so calls
+ * a message is printed and non-zero returned (at rank 128: 1024 chunks x 14 timesteps fit, 15
+ * do not). The first call on a device resolves the array's device address and configures the
+ * kernels of its shape and mode: make it before any stream capture begins. All calls share the array, so calls
  * whose kernels overlap on the GPU race; run one such layer at a time per device. */
 #define FLUKE_LSTM_NOALLOC_SCRATCH_BYTES (4u << 20)
 int fluke_factored_lstm_layer_i8_noalloc_gpu(const fluke_flstm_layer_t *layer);

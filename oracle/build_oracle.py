@@ -75,10 +75,13 @@ def build_reference(ref_dir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-dir", default="/root/reference")
+    ap.add_argument("--ref-dir", default=os.environ.get("FLUKE_REFERENCE_DIR", ""),
+                    help="checkout of the reference project (or set FLUKE_REFERENCE_DIR); without it only "
+                         "oracle/liboracle.so is built")
     args = ap.parse_args()
     build_port()
-    build_reference(args.ref_dir)
+    if args.ref_dir:
+        build_reference(args.ref_dir)
 
 
 if __name__ == "__main__":

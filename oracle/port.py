@@ -20,8 +20,7 @@ def lib():
     if _LIB is None:
         src = os.path.join(HERE, "fluke_oracle.c")
         if not os.path.isfile(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
-            subprocess.run([sys.executable, os.path.join(HERE, "build_oracle.py"), "--ref-dir", "/nonexistent"],
-                           check=True, stdout=subprocess.DEVNULL)
+            subprocess.run([sys.executable, os.path.join(HERE, "build_oracle.py")], check=True, stdout=subprocess.DEVNULL)
         _LIB = ctypes.CDLL(_SO)
         _LIB.orc_e4m3_decode.restype = F
         _LIB.orc_e4m3_decode.argtypes = [ctypes.c_uint8]
@@ -227,6 +226,13 @@ def down_proj(a, w, sa, sb, const_sa=1.0 / 127.0):
     _call("orc_down_proj", a, w, None if sa is None else _c(sa, np.float32), float(np.float32(const_sa)),
           _c(sb, np.float32), out, a.shape[0], w.shape[0], a.shape[1])
     return out
+
+
+def down_proj_fp8(a, w_nk, sa, sb):
+    """fp8 down-projection of the fp8 stack: the base fp8 GEMM with N = R, K = H, out f16 =
+    (acc * sa[m]) * sb[n] (fly/rdna4/factored_lstm/export_fp8_factored_lstm.py:161-181; epilogue
+    fly/rdna4/gemm/rdna_fp8_preshuffle_gemm.py:379-393). a [M,K] and w_nk [N,K] are e4m3 bytes."""
+    return epi_dequant2(gemm_fp8_f32(a, w_nk), sa, sb)
 
 
 def lstm_step(A, W4, bias4, c):

@@ -37,6 +37,27 @@ int fluke_factored_lstm_step_i8_gpu(const void *A, const void *W_i, const void *
     return fluke_host_note_error(fluke_sm100_lstm_step(&s, fluke_host_stream()));
 }
 
+/* fp8 export's down-projection and step (fly/rdna4/factored_lstm/export_fp8_factored_lstm.py:113-181) */
+int fluke_down_proj_fp8_gpu(void *out_f16, int ld_out, const void *a_fp8, const void *w_fp8_nk,
+                            const void *scale_a, const void *scale_b, int M, int N, int K) {
+    fluke_sm100_gemm_t g = {0};
+    g.kind = FLUKE_SM100_KIND_F8;
+    g.epilogue = FLUKE_SM100_EPI_DEQUANT2;
+    g.M = M; g.N = N; g.K = K;
+    g.a = a_fp8; g.b = w_fp8_nk; g.out = out_f16; g.ld_out = ld_out;
+    g.scale_a = (const float *)scale_a;
+    g.scale_b = (const float *)scale_b;
+    if (!scale_a) return fluke_host_note_error(1 /* cudaErrorInvalidValue */);
+    return fluke_host_note_error(fluke_sm100_gemm(&g, fluke_host_stream()));
+}
+
+int fluke_factored_lstm_step_fp8_gpu(const void *A, const void *W_i, const void *W_f,
+                                     const void *W_g, const void *W_o, const void *bias_i,
+                                     const void *bias_f, const void *bias_g, const void *bias_o,
+                                     void *c, void *h_out, int B, int H, int Kc) {
+    return fluke_factored_lstm_step_i8_gpu(A, W_i, W_f, W_g, W_o, bias_i, bias_f, bias_g, bias_o, c, h_out, B, H, Kc);
+}
+
 size_t fluke_factored_lstm_layer_workspace(int T, int B, int H, int R) {
     return fluke_sm100_lstm_layer_workspace(T, B, H, R);
 }

@@ -1,7 +1,7 @@
 """Generate tests/golden/reference_tests.npz by IMPORTING the reference's own Python test
 modules and calling their reference functions on the CPU.
 
-    python tests/golden/make_golden_from_reference_tests.py [--ref-dir /root/reference]
+    python tests/golden/make_golden_from_reference_tests.py --ref-dir <reference checkout>
 
 Runs only where the reference checkout is mounted (the build machine); the resulting fixture
 is committed and is what the test-suite reads. `.cuda()` is patched to the identity so the
@@ -11,6 +11,7 @@ helpers of the fp8 modules import. Inputs are drawn exactly as each reference te
 """
 import argparse
 import importlib
+import importlib.util
 import os
 import sys
 import types
@@ -24,7 +25,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-dir", default="/root/reference")
+    ap.add_argument("--ref-dir", default=os.environ.get("FLUKE_REFERENCE_DIR"), required=os.environ.get("FLUKE_REFERENCE_DIR") is None,
+                    help="checkout of the reference project (or set FLUKE_REFERENCE_DIR)")
     ref = ap.parse_args().ref_dir
     for sub in ("fly/rdna4/gemm", "fly/rdna4/rotary", "test", "", "cute"):  # cute/ first: its common.py
         sys.path.insert(0, os.path.join(ref, sub))
@@ -129,6 +131,31 @@ def main():
     # the pre-shuffled layout itself, on a small weight
     small = B8[:64, :48].contiguous()
     out.update(fp8_small_kn=T(small.view(torch.uint8)), fp8_small_shuffled=T(fg.preshuffle_b_fp8(small).contiguous()))
+
+    # ---- fly/test_factored_lstm.py: torch reference of the fp8 stack's fused step (:38-47), inputs
+    # drawn as the test draws them (:60-66) at a smaller hidden size to keep the fixture small -----
+    spec = importlib.util.spec_from_file_location("fly_test_factored_lstm", os.path.join(ref, "fly", "test_factored_lstm.py"))
+    fl = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(fl)
+    torch.manual_seed(0)
+    M, Hs, Kc = 64, 128, fl.Kc
+    A = (torch.randn(M, Kc) * 0.3).to(torch.float16)
+    Bs = [(torch.randn(Hs, Kc) * 0.3).to(torch.float16) for _ in range(4)]
+    biases = [torch.randn(Hs) * 0.1 for _ in range(4)]
+    cell0 = torch.randn(M, Hs) * 0.5
+    c_ref, h_ref = fl.reference(A, Bs, biases, cell0)
+    out.update(flstm8_A=T(A), flstm8_W=T(torch.cat(Bs, 0)), flstm8_bias=T(torch.cat(biases, 0)), flstm8_c0=T(cell0),
+               flstm8_c_ref=T(c_ref), flstm8_h_ref=T(h_ref))
+    # ---- fp8 down-projection: the base fp8 GEMM of rdna_fp8_preshuffle_gemm.py with N = R, K = H
+    # (export_fp8_factored_lstm.py:161-181); reference as fly/test_rotary.py builds its GEMM (:88-90) --
+    torch.manual_seed(7)
+    hx = torch.randn(48, 768) * 0.3
+    dn = torch.randn(768, 128) / 768 ** 0.5            # [K, N] as the fly helpers take it
+    h8, sh = fg.fp8_quantize_per_token(hx)
+    d8, sd = fg.fp8_quantize_per_channel(dn)
+    dp = (h8.float() * sh[:, None]) @ (d8.float() * sd[None, :])
+    out.update(dp8_A=T(h8.view(torch.uint8)), dp8_sa=T(sh), dp8_B_kn=T(d8.view(torch.uint8)), dp8_sb=T(sd),
+               dp8_expected=T(dp).astype(np.float16))
 
     path = os.path.join(HERE, "reference_tests.npz")
     np.savez_compressed(path, **out)

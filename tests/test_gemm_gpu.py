@@ -337,6 +337,36 @@ def test_fp8_base_gemm_vs_oracle():
     assert np.abs(got - exp).max() <= TOL_REL_RMS * np.sqrt((exp ** 2).mean())
 
 
+def test_rmsnorm_quant_then_qkv_back_to_back_at_config_size(be):
+    """The chain a transformer block runs: fluke_rmsnorm_quant_int8_gpu writes the int8 activations
+    and their row scales, fluke_qkv_rotary_i8_gpu consumes them, on four buffer sets one after the
+    other ([32000, 512] each, more than L2 in total). Sampled rows of every set against the oracle
+    chain; the f16 output is bit-exact because both kernels are."""
+    n, h, sets = 32000, 512, 4
+    g = torch.Generator().manual_seed(31)
+    w = (1 + 0.1 * torch.randn(h, generator=g)).half()
+    wq, sq = prep.quantize_int8_rows(torch.randn(1536, 512, generator=g) * 0.02)
+    sin, cos = prep.rotary_tables(1000, 64)
+    xs = [torch.randn(n, h, generator=g).half() for _ in range(sets)]
+    W, WQ, SQ, SIN, COS = w.to(DEV), wq.to(DEV), sq.to(DEV), sin.to(DEV), cos.to(DEV)
+    X = [x.to(DEV) for x in xs]
+    q8 = [torch.zeros(n, h, dtype=torch.int8, device=DEV) for _ in range(sets)]
+    s8 = [torch.ones(n, device=DEV) for _ in range(sets)]
+    outs = []
+    for i in range(sets):
+        ops.rmsnorm_quant_int8(X[i], W, q8[i], s8[i], 0.0, 1e-5)
+        outs.append(ops.qkv_rotary_i8(be, q8[i], WQ, s8[i], SQ, SIN, COS, 1000))
+    rows = _sample_rows(n, 1000, 3)[::4]
+    pos = rows % 1000
+    for i in range(sets):
+        oq, osc = port.rmsnorm_quant(xs[i][rows].numpy(), w.numpy(), np.zeros((len(rows), h), np.int8), np.ones(len(rows), np.float32), 0.0, 1e-5)
+        gq = q8[i][rows.to(DEV)].cpu().numpy()
+        assert np.abs(gq.astype(np.int32) - oq.astype(np.int32)).max() <= 1      # rsqrt: within one code of the CPU oracle
+        exp = port.epi_rotary(port.gemm_i8_s32(gq, wq.numpy()), s8[i][rows.to(DEV)].cpu().numpy(), sq.numpy(),
+                              sin[pos].numpy(), cos[pos].numpy(), len(rows), 1024)
+        assert np.array_equal(outs[i][rows.to(DEV)].cpu().numpy().view(np.uint16), exp.view(np.uint16))
+
+
 def test_quant_kernel_feeds_the_gemm(be):
     """fluke_quant_int8_gpu output (amax/128 convention) straight into the fused kernel."""
     g = torch.Generator().manual_seed(13)

@@ -57,6 +57,52 @@ def test_step_golden_from_reference_test(golden_tests):
     assert (h.float().cpu() / 127.0 - torch.from_numpy(g["lstm_h_ref"])).abs().max() < 0.08
 
 
+def test_fp8_export_step_golden_from_fly_reference_test(golden_tests):
+    """The fused step of the reference's fp8 export (fly/rdna4/factored_lstm/rdna_fp8_factored_lstm.py)
+    against the torch reference of fly/test_factored_lstm.py on inputs drawn as that test draws
+    them; its bar (:66-72): cell < 1e-2, every int8 code within one level."""
+    g = golden_tests
+    T = lambda k: torch.from_numpy(np.ascontiguousarray(g[k])).to(DEV)
+    c = T("flstm8_c0")
+    h = ops.factored_lstm_step_i8(T("flstm8_A"), T("flstm8_W"), T("flstm8_bias"), c, fp8_export_name=True)
+    assert (c.cpu() - torch.from_numpy(g["flstm8_c_ref"])).abs().max() < 1e-2
+    d = (h.cpu().int() - torch.from_numpy(g["flstm8_h_ref"]).int()).abs()
+    assert int(d.max()) <= 1
+    # and the oracle on the same inputs: same bar against the reference, tighter against the kernel
+    ce, he = port.lstm_step(g["flstm8_A"], g["flstm8_W"], g["flstm8_bias"], g["flstm8_c0"])
+    assert np.abs(ce - g["flstm8_c_ref"]).max() < 1e-2 and np.abs(he.astype(np.int32) - g["flstm8_h_ref"].astype(np.int32)).max() <= 1
+    assert np.abs(c.cpu().numpy() - ce).max() < 1e-4
+
+
+@pytest.mark.parametrize("M", [48, 128, 1024, 300])
+def test_fp8_down_projection_vs_oracle_and_fly_reference(golden_tests, M):
+    """fluke_down_proj_fp8_gpu (N = R = 128, K = H = 768): against the oracle within 1e-2 of the
+    output RMS (f32 accumulation order), against the reference construction of the fly tests
+    within their 5e-2, and into a wider buffer (row stride)."""
+    gt = golden_tests
+    if M == 48:   # the fixture built with the reference's own fp8 quantisers
+        a8, sa = torch.from_numpy(gt["dp8_A"]), torch.from_numpy(gt["dp8_sa"])
+        w8 = torch.from_numpy(np.ascontiguousarray(gt["dp8_B_kn"].T)); sb = torch.from_numpy(gt["dp8_sb"])
+    else:
+        g = torch.Generator().manual_seed(M)
+        a, sa = prep.quantize_fp8_rows(torch.randn(M, 768, generator=g) * 0.3)
+        w, sb = prep.quantize_fp8_rows(torch.randn(128, 768, generator=g) / 768 ** 0.5)
+        a8, w8 = a.view(torch.uint8), w.view(torch.uint8)
+    buf = torch.full((M, 256), 3.0, dtype=torch.float16, device=DEV)
+    ops.down_proj_fp8(a8.to(DEV), w8.to(DEV), sa.to(DEV), sb.to(DEV), out=buf[:, :128])
+    got = buf[:, :128].float().cpu().numpy()
+    assert bool((buf[:, 128:] == 3.0).all())
+    exp = port.down_proj_fp8(a8.numpy(), w8.numpy(), sa.numpy(), sb.numpy()).astype(np.float32)
+    assert np.abs(got - exp).max() <= 1e-2 * np.sqrt((exp ** 2).mean())
+    if M == 48:
+        assert np.abs(got - gt["dp8_expected"].astype(np.float32)).max() < 5e-2
+    # a preshuffled weight, as the fp8 ABI passes it, goes through the re-ordering kernel once
+    wsh = prep.preshuffle_fp8_weight(w8)
+    plain = ops.fp8_unshuffle(wsh.to(DEV), 128, 768)
+    again = ops.down_proj_fp8(a8.to(DEV), plain, sa.to(DEV), sb.to(DEV))
+    assert torch.equal(again, buf[:, :128])
+
+
 def test_hidden_quantiser_rounds_half_away_from_zero():
     """Gates forced open (large o bias, zero weights): h = tanh(c); codes at +-k.5/127 round away."""
     B, H, Kc = 128, 64, 64
