@@ -493,6 +493,20 @@ def bench_ops(torch, peaks, tensor_peaks, gpu_index):
         ops.qkv_rotary_i8(be, a8[0][0], wq, a8[0][1], sq, sin, cos, 1000, out=o3[0])
         o3p.copy_(o3[0], non_blocking=True)
     out["qkv_rotary_i8_cfg3"]["e2e"] = e2e(qkv_e2e, n * 512 + n * 4, n * 1536 * 2)
+    # the chain of a transformer block: RMSNorm + int8 quantisation, then the QKV GEMM on what it
+    # wrote (three rotating buffer sets, 147 MB each): per (norm, GEMM) pair
+    xc = [torch.randn(n, h, generator=g).half().to(dev) for _ in range(3)]
+    qc = [torch.zeros(n, h, dtype=torch.int8, device=dev) for _ in range(3)]
+    sc_ = [torch.ones(n, device=dev) for _ in range(3)]
+    chain = []
+    for i in range(3):
+        chain += [lambda i=i: ops.rmsnorm_quant_int8(xc[i], w, qc[i], sc_[i], 0.0, 1e-5),
+                  lambda i=i: ops.qkv_rotary_i8(be, qc[i], wq, sc_[i], sq, sin, cos, 1000, out=o3[i])]
+    ms_pair = time_rotating(chain, 10, torch) * 2
+    out["rmsnorm_quant_then_qkv_chain"] = {"us": round(ms_pair * 1e3, 2),
+                                           "sum_of_the_two_alone_us": round(out["rmsnorm_quant_int8_cfg2"]["us"] + out["qkv_rotary_i8_cfg3"]["us"], 2),
+                                           "note": "the GEMM's int8 activations come from L2 (profiles/rmsnorm_quant_qkv_chain_ncu_summary.md)"}
+    del xc, qc, sc_
 
     # ---- config 4: dual GEMM + SiLU ------------------------------------------------------------------------
     wg_h, sg_h = prep.quantize_int8_rows(torch.randn(2048, 512, generator=g) * 0.02)

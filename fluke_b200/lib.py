@@ -78,6 +78,8 @@ SIGNATURES = {
     "fluke_down_proj_i8_gpu": (I, [P, I, P, P, P, P, I, I, I]),
     "fluke_factored_lstm_step_i8_gpu": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I]),
     "fluke_down_proj_fp8_gpu": (I, [P, I, P, P, P, P, I, I, I]),
+    "fluke_down_proj_i8_stream_gpu": (I, [P, I, P, P, P, P, I, I, I, P]),
+    "fluke_factored_lstm_step_i8_stream_gpu": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, P]),
     "fluke_factored_lstm_step_fp8_gpu": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I]),
     "fluke_factored_lstm_layer_workspace": (Z, [I, I, I, I]),
     "fluke_factored_lstm_layer_i8_gpu": (I, [ctypes.POINTER(fluke_flstm_layer_t)]),

@@ -367,6 +367,23 @@ int fluke_factored_lstm_step_i8_gpu(
     int B, int H, int Kc
 );
 
+/* The two per-step entry points again with the stream as a trailing argument, as the reference's
+ * exports take it (cute/ampere/gemm/gemm_i8_quant.py:237-239,
+ * cute/ampere/factored_lstm/factored_lstm_i8.py:98-99: a CUstream, so that a caller can capture its
+ * own per-timestep loop); NULL = the legacy default stream. The forms without it use the calling
+ * thread's fluke_set_stream setting. */
+int fluke_down_proj_i8_stream_gpu(
+    void *out_f16, int ld_out, const void *a_i8, const void *w_i8,
+    const void *scale_a, const void *scale_b, int M, int N, int K, void *stream
+);
+int fluke_factored_lstm_step_i8_stream_gpu(
+    const void *A,
+    const void *W_i, const void *W_f, const void *W_g, const void *W_o,
+    const void *bias_i, const void *bias_f, const void *bias_g, const void *bias_o,
+    void *c, void *h_out,
+    int B, int H, int Kc, void *stream
+);
+
 /* The two kernels of the reference's fp8 factored-LSTM export
  * (fly/rdna4/factored_lstm/export_fp8_factored_lstm.py).
  *   fluke_down_proj_fp8_gpu          its down-projection (:161-181, `down_proj_fp8_R{R}_K{H}`): the fp8

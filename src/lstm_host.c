@@ -7,8 +7,9 @@
 
 #include "gpu_common.h"
 
-int fluke_down_proj_i8_gpu(void *out_f16, int ld_out, const void *a_i8, const void *w_i8,
-                           const void *scale_a, const void *scale_b, int M, int N, int K) {
+int fluke_down_proj_i8_stream_gpu(void *out_f16, int ld_out, const void *a_i8, const void *w_i8,
+                                  const void *scale_a, const void *scale_b, int M, int N, int K,
+                                  void *stream) {
     fluke_sm100_gemm_t g = {0};
     g.kind = FLUKE_SM100_KIND_I8;
     g.epilogue = FLUKE_SM100_EPI_DEQUANT;
@@ -17,13 +18,18 @@ int fluke_down_proj_i8_gpu(void *out_f16, int ld_out, const void *a_i8, const vo
     g.scale_a = (const float *)scale_a;
     g.const_scale_a = 1.0f / 127.0f;
     g.scale_b = (const float *)scale_b;
-    return fluke_host_note_error(fluke_sm100_gemm(&g, fluke_host_stream()));
+    return fluke_host_note_error(fluke_sm100_gemm(&g, stream));
 }
 
-int fluke_factored_lstm_step_i8_gpu(const void *A, const void *W_i, const void *W_f,
-                                    const void *W_g, const void *W_o, const void *bias_i,
-                                    const void *bias_f, const void *bias_g, const void *bias_o,
-                                    void *c, void *h_out, int B, int H, int Kc) {
+int fluke_down_proj_i8_gpu(void *out_f16, int ld_out, const void *a_i8, const void *w_i8,
+                           const void *scale_a, const void *scale_b, int M, int N, int K) {
+    return fluke_down_proj_i8_stream_gpu(out_f16, ld_out, a_i8, w_i8, scale_a, scale_b, M, N, K, fluke_host_stream());
+}
+
+int fluke_factored_lstm_step_i8_stream_gpu(const void *A, const void *W_i, const void *W_f,
+                                           const void *W_g, const void *W_o, const void *bias_i,
+                                           const void *bias_f, const void *bias_g, const void *bias_o,
+                                           void *c, void *h_out, int B, int H, int Kc, void *stream) {
     fluke_sm100_lstm_step_t s = {0};
     s.B = B; s.H = H; s.Kc = Kc;
     s.a_lo = A; s.ld_a_lo = Kc; s.k_lo = Kc;
@@ -34,7 +40,15 @@ int fluke_factored_lstm_step_i8_gpu(const void *A, const void *W_i, const void *
     s.bias[2] = (const float *)bias_g; s.bias[3] = (const float *)bias_o;
     s.c = (float *)c;
     s.h_out = (int8_t *)h_out;
-    return fluke_host_note_error(fluke_sm100_lstm_step(&s, fluke_host_stream()));
+    return fluke_host_note_error(fluke_sm100_lstm_step(&s, stream));
+}
+
+int fluke_factored_lstm_step_i8_gpu(const void *A, const void *W_i, const void *W_f,
+                                    const void *W_g, const void *W_o, const void *bias_i,
+                                    const void *bias_f, const void *bias_g, const void *bias_o,
+                                    void *c, void *h_out, int B, int H, int Kc) {
+    return fluke_factored_lstm_step_i8_stream_gpu(A, W_i, W_f, W_g, W_o, bias_i, bias_f, bias_g, bias_o, c, h_out, B, H,
+                                                  Kc, fluke_host_stream());
 }
 
 /* fp8 export's down-projection and step (fly/rdna4/factored_lstm/export_fp8_factored_lstm.py:113-181) */

@@ -103,6 +103,41 @@ def test_fp8_down_projection_vs_oracle_and_fly_reference(golden_tests, M):
     assert torch.equal(again, buf[:, :128])
 
 
+def test_per_step_entry_points_with_an_explicit_stream(flib):
+    """The `_stream` forms of the two per-step kernels launch on the stream they are given (here a
+    side stream while the thread's own setting stays the default stream) and give the bytes of the
+    forms without it; a step loop driven this way equals the layer entry point's per-step mode."""
+    T, B, H, R = 4, 200, 768, 128
+    layer, x, xs = _layer_case(T, B, H, R, 21, False)
+    X, XS = x.to(DEV), xs.to(DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    c = torch.zeros(B, H, device=DEV); h = torch.zeros(B, H, dtype=torch.int8, device=DEV)
+    A = torch.empty(B, 2 * R, dtype=torch.float16, device=DEV)
+    outs = []
+    w = [layer.w_up.data_ptr() + g * H * 2 * R * 2 for g in range(4)]
+    bs = [layer.bias.data_ptr() + g * H * 4 for g in range(4)]
+    assert flib.fluke_get_stream() is None
+    with torch.cuda.stream(side):
+        for t in range(T):
+            assert flib.fluke_down_proj_i8_stream_gpu(A.data_ptr(), 2 * R, h.data_ptr(), layer.dn_hh.data_ptr(), 0,
+                                                      layer.dn_hh_scale.data_ptr(), B, R, H, side.cuda_stream) == 0
+            assert flib.fluke_down_proj_i8_stream_gpu(A.data_ptr() + 2 * R, 2 * R, X[t].data_ptr(), layer.dn_ih.data_ptr(),
+                                                      XS[t * B:(t + 1) * B].data_ptr(), layer.dn_ih_scale.data_ptr(), B, R, H,
+                                                      side.cuda_stream) == 0
+            hn = torch.empty(B, H, dtype=torch.int8, device=DEV)
+            assert flib.fluke_factored_lstm_step_i8_stream_gpu(A.data_ptr(), w[0], w[1], w[2], w[3], bs[0], bs[1], bs[2], bs[3],
+                                                               c.data_ptr(), hn.data_ptr(), B, H, 2 * R, side.cuda_stream) == 0
+            h = hn
+            outs.append(hn)
+    side.synchronize()
+    flib.fluke_set_lstm_persistent(0)
+    c2 = torch.zeros(B, H, device=DEV); h2 = torch.zeros(B, H, dtype=torch.int8, device=DEV)
+    want = ops.factored_lstm_layer_i8(X, XS, layer.dn_ih, layer.dn_ih_scale, layer.dn_hh, layer.dn_hh_scale, layer.w_up, layer.bias, c2, h2)
+    flib.fluke_set_lstm_persistent(1)
+    assert torch.equal(torch.stack(outs), want) and torch.equal(c, c2)
+
+
 def test_hidden_quantiser_rounds_half_away_from_zero():
     """Gates forced open (large o bias, zero weights): h = tanh(c); codes at +-k.5/127 round away."""
     B, H, Kc = 128, 64, 64
