@@ -8,7 +8,13 @@ alternating direction, hidden 768, factor rank 128, T = 1000 timesteps, 1024 chu
 path). One "step" = one pass of the whole stack over one [T, B, 768] int8 batch.
 
     value            chunk-timesteps per second per layer, summed over GPUs
-                     = n_gpus * B * T * layers / step_time   (inputs resident in HBM)
+                     = n_gpus * B * T * layers / step_time   (inputs resident in HBM). The K steps
+                     are independent passes over 1024-chunk batches; they run two at a time, side
+                     by side in one [T, 2048, H] layer launch (chunks are independent: the bytes are
+                     those of separate passes, tested), because the recurrence is a latency chain
+                     whose step time barely depends on the rows in flight and one launch holds 16
+                     row tiles; an odd last step runs alone. `one_pass_per_launch` beside it is
+                     the same measurement with every step in a launch of its own.
     e2e              the same through the library's C streaming handle (fluke_flstm_stream_*, bound by
                      fluke_b200.lstm.StackPipeline) with HOST buffers: every step copies its input
                      from pinned host memory and its output back, all inside the timed region; the
@@ -19,12 +25,10 @@ path). One "step" = one pass of the whole stack over one [T, B, 768] int8 batch.
     strong           the north star's own wording: 1024 chunks IN TOTAL sharded over the GPUs
                      (fluke_b200.shard.shard_range), same timing rule; at N = 1 it is `value`
     saturation       (N = 1) recurrence time per step of one layer against the batch size
-    two_passes_per_launch   `value`'s measurement repeated with two resident batches per layer
-                     launch (what e2e does, without the copies); reported beside, not as, `value`
-    roofline         the persistent LSTM recurrence kernel (tensor bound): algorithmic FLOPs per
-                     launch / its launch duration, measured with CUDA events on the launching
-                     stream, against the measured bf16 GEMM peak of this pool; `traffic` from the
-                     ncu capture recorded in profiles/lstm_recurrence_traffic.json
+    roofline         the persistent LSTM recurrence kernel of the timed region (tensor bound):
+                     algorithmic FLOPs per launch / its launch duration, measured with CUDA events
+                     on the launching stream, against the measured bf16 GEMM peak of this pool;
+                     `traffic` from the ncu capture recorded in profiles/lstm_recurrence_traffic.json
     cpu_baseline     the CPU oracle (oracle/fluke_oracle.c, a port: the reference has no CPU
                      implementation of the LSTM contraction) on a bounded sample, all host cores;
                      the rate is extrapolated to the full workload
@@ -104,15 +108,16 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
 
 
-def recurrence_traffic(kernel_name):
-    """DRAM bytes per step of the recurrence kernel, from the ncu capture recorded under profiles/."""
+def recurrence_traffic(kernel_name, row_tiles):
+    """DRAM bytes per step of the recurrence kernel launched over `row_tiles` tiles of 128 chunks, from
+    the ncu capture recorded under profiles/."""
     path = os.path.join(ROOT, "profiles", "lstm_recurrence_traffic.json")
     try:
         rec = json.load(open(path))
     except (OSError, ValueError):
         return None
     for k in rec.get("kernels", []):
-        if k["kernel"] == kernel_name:
+        if k["kernel"] == kernel_name and k.get("row_tiles") == row_tiles:
             return k
     return None
 
@@ -636,14 +641,30 @@ def run_ours(args):
         barrier()
         return reduce_step_time(e0.elapsed_time(e1) / steps)
 
+    # two batches side by side: what a launch of the timed region works on
+    x2, xs2 = torch.cat([x_dev, x_dev], dim=1), torch.cat([xs_dev.view(T, B)] * 2, dim=1).reshape(-1)
+    bufs2 = [torch.empty(T, 2 * B, H, dtype=torch.int8, device=dev) for _ in range(2)]
+    ws2 = torch.empty(L.fluke_factored_lstm_layer_workspace(T, 2 * B, H, R), dtype=torch.uint8, device=dev)
+
+    def step_pair():
+        return run_stack(layers, x2, xs2, state=fresh_state(2 * B), workspace=ws2, buffers=bufs2)[0]
+
+    def run_steps(k):
+        """k independent passes: two per layer launch, an odd last one alone."""
+        for _ in range(k // 2):
+            step_pair()
+        if k % 2:
+            step_resident()
+
     # ---- headline: weak scaling, inputs resident ------------------------------------------------------
-    for _ in range(args.warmup):
-        step_resident()
+    run_steps(max(args.warmup, 3))
+    step_resident()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = timed(step_resident, args.steps)
+    ms = timed(lambda: run_steps(args.steps), 1) / args.steps
     clocks = sampler.stop() if rank == 0 else None
+    ms_single = timed(step_resident, min(args.steps, 8))           # every step in a launch of its own
 
     # ---- strong scaling: 1024 chunks in total, sharded ------------------------------------------------
     if world > 1:
@@ -660,7 +681,7 @@ def run_ours(args):
         ms_strong = timed(step_strong, args.steps)
         del xs_sh, ss_sh, bufs_sh
     else:
-        ms_strong = ms
+        ms_strong = ms_single
 
     # ---- end to end: host buffers in the timed region, through the C streaming handle --------------------
     pipe = StackPipeline(layers, T, B, dev, passes_per_launch=2, time_chunks=4)
@@ -691,19 +712,8 @@ def run_ours(args):
     ms_copy = timed(copy_only, args.steps, after=copy_done)
     torch.cuda.empty_cache()
 
-    # ---- the resident measurement again with two batches side by side in each layer launch -------------
-    x2, xs2 = torch.cat([x_dev, x_dev], dim=1), torch.cat([xs_dev.view(T, B)] * 2, dim=1).reshape(-1)
-    bufs2 = [torch.empty(T, 2 * B, H, dtype=torch.int8, device=dev) for _ in range(2)]
-    ws2 = torch.empty(L.fluke_factored_lstm_layer_workspace(T, 2 * B, H, R), dtype=torch.uint8, device=dev)
-
-    def step_pair():
-        return run_stack(layers, x2, xs2, state=fresh_state(2 * B), workspace=ws2, buffers=bufs2)[0]
-
-    step_pair()
-    pairs = max(1, args.steps // 2)
-    ms_pair = timed(step_pair, pairs) / 2.0                    # per pass
-    # its recurrence kernel (the wide configuration: 16 row tiles in one launch), timed like the
-    # headline kernel below: layer minus x_down GEMM
+    # the recurrence kernel of the timed region (the wide configuration: 16 row tiles in one launch):
+    # layer minus x_down GEMM, both from CUDA events
     lay0 = layers[0]
     st2 = (torch.zeros(2 * B, H, dtype=torch.float32, device=dev), torch.zeros(2 * B, H, dtype=torch.int8, device=dev))
 
@@ -720,6 +730,8 @@ def run_ours(args):
         e1.record()
         torch.cuda.synchronize()
         us_pair[mask] = e0.elapsed_time(e1) / 2 * 1e3
+        if mask == 7:
+            form_pair = L.fluke_sm100_lstm_last_form()
     del x2, xs2, bufs2, ws2, st2
     status = flib.read_status()
     if status != 0:
@@ -752,32 +764,40 @@ def run_ours(args):
             e1.record()
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) / reps * 1e3   # microseconds
-        us_layer, us_xdown = layer_us(x_dev, xs_dev, B, 7), layer_us(x_dev, xs_dev, B, 1)
-        form = L.fluke_sm100_lstm_last_form()
-        kname = {1: "lstm_cluster_kernel", 2: "lstm_persist_kernel"}.get(form, "lstm_step_kernel")
-        per_kernel = {"layer_total": us_layer, "x_down_gemm": us_xdown, kname: us_layer - us_xdown}
-        flops = T * (2.0 * B * (2 * R) * (4 * H) + 2.0 * B * R * H)   # f16 gate contraction + int8 hh projection
-        achieved = flops / (per_kernel[kname] * 1e-6) / 1e12
-        tr = recurrence_traffic(kname)
-        traffic = None if tr is None else tr["dram_read_bytes_per_step"] * T + float(T) * B * H
-        roofline = {"kernel": kname, "bound": "tensor", "achieved": round(achieved, 2),
+        flops = T * (2.0 * B * (2 * R) * (4 * H) + 2.0 * B * R * H)   # per 1024-chunk layer: f16 gate contraction + int8 hh projection
+
+        def roofline_of(us_layer, us_xdown, form, batches):
+            kname = {1: "lstm_cluster_kernel", 2: "lstm_persist_kernel"}.get(form, "lstm_step_kernel")
+            us_k = us_layer - us_xdown
+            achieved = batches * flops / (us_k * 1e-6) / 1e12
+            tr = recurrence_traffic(kname, batches * ((B + 127) // 128))
+            return {"kernel": kname, "bound": "tensor", "achieved": round(achieved, 2),
                     "peak": peaks["tf_sustained"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tf_sustained"], 4),
                     "peak_source": f"{peaks['source']} bf16 GEMM, sustained",
-                    "traffic": traffic,
+                    "chunks_per_launch": batches * B,
+                    "traffic": None if tr is None else tr["dram_read_bytes_per_step"] * T + float(T) * batches * B * H,
                     "traffic_source": None if tr is None else
                     f"profiles/lstm_recurrence_traffic.json: {tr['dram_read_bytes_per_step']:.0f} B read per step (ncu, T={tr['T_captured']}) "
                     "x T, plus the h_out the launch writes (larger than L2)",
-                    "flops_per_launch": flops, "us_per_launch": {k: round(v, 3) for k, v in per_kernel.items()},
-                    "cycles_per_step": round(per_kernel[kname] / T * (clocks["sm_mhz"] or 0), 0) if clocks else None}
+                    "flops_per_launch": batches * flops,
+                    "us_per_launch": {"layer_total": round(us_layer, 3), "x_down_gemm": round(us_xdown, 3), kname: round(us_k, 3)},
+                    "cycles_per_step": round(us_k / T * (clocks["sm_mhz"] or 0), 0) if clocks else None}
+        roofline = roofline_of(us_pair[7], us_pair[1], form_pair, 2)
+        us_layer, us_xdown = layer_us(x_dev, xs_dev, B, 7), layer_us(x_dev, xs_dev, B, 1)
+        roofline_single = roofline_of(us_layer, us_xdown, L.fluke_sm100_lstm_last_form(), 1)
         cpu_v, cores, sample = cpu_lstm_sample()
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f16",
             "data": "synthetic",
             "config": {"workload": "factored int8 LSTM stack: 5 layers alternating direction, T=1000, H=768, rank=128, "
-                                   f"{B} chunks per GPU", "l2": "inputs larger than L2 (786 MB per layer input)",
-                       "parallelism": f"dp{world} (independent chunks, no collective)"},
+                                   f"{B} chunks per GPU per step", "l2": "inputs larger than L2 (786 MB per layer input)",
+                       "parallelism": f"dp{world} (independent chunks, no collective)",
+                       "steps_per_launch": "2: the K independent steps run two at a time, side by side in one [T, 2048, H] "
+                                           "layer launch (16 row tiles); one_pass_per_launch is the figure with one step per launch"},
             "timesteps_per_sec_per_gpu_per_layer": T * NL / (ms * 1e-3),
+            "one_pass_per_launch": {"value": units / (ms_single * 1e-3), "unit": UNIT, "ms_per_step": ms_single,
+                                    "roofline": roofline_single},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() + xs_host.numel() * 4, "d2h_bytes_per_step": out_host.numel(),
                     "passes_per_launch": 2, "time_chunks": 4, "api": "fluke_flstm_stream_* (C handle)",
@@ -787,13 +807,7 @@ def run_ours(args):
                                   "note": "the step's copies alone, both directions at once, all ranks at once, no kernels"},
                     "frac_of_copy_ceiling": ms_copy / ms_e2e},
             "strong": strong_scaling_record(CHUNKS_PER_GPU, world, ms_strong),
-            "two_passes_per_launch": {"value": units / (ms_pair * 1e-3), "unit": UNIT, "ms_per_step": ms_pair,
-                                      "note": "two resident batches of 1024 chunks side by side in each layer launch",
-                                      "recurrence_kernel_us": round(us_pair[7] - us_pair[1], 3),
-                                      "recurrence_kernel_tflops": round(2 * flops / ((us_pair[7] - us_pair[1]) * 1e-6) / 1e12, 2),
-                                      "recurrence_kernel_frac": round(2 * flops / ((us_pair[7] - us_pair[1]) * 1e-6) / 1e12
-                                                                      / peaks["tf_sustained"], 4)},
-            "gpu_launches": args.steps * NL * 2,   # per layer: x_down GEMM + persistent recurrence
+            "gpu_launches": (args.steps // 2 + args.steps % 2) * NL * 2,   # per layer call: x_down GEMM + persistent recurrence
             "clocks": clocks, "roofline": roofline,
             "cpu_baseline": {"value": cpu_v, "unit": "chunk-timesteps/s (per layer)", "cores": cores, "kind": "port",
                              "sample": sample, "extrapolated": True,
