@@ -230,7 +230,8 @@ def time_rotating(calls, iters, torch, sustain_s=0.0, gpu_index=0):
     own 10-20 us). Falls back to timing the Python loop if the capture fails.
     With sustain_s > 0 the graph is also replayed back to back for that long with the SM clock
     sampled, and (ms, sustained_ms, clocks) is returned: the figure under the clock the kernel
-    itself pulls."""
+    itself pulls; clocks["burst_sm_mhz"] is the clock during one more replay of the timed burst,
+    measured from inside the GPU (GpuClockProbe)."""
     from fluke_b200 import lib as flib
     L = flib.load()
     for c in calls:
@@ -277,6 +278,14 @@ def time_rotating(calls, iters, torch, sustain_s=0.0, gpu_index=0):
     ms = e0.elapsed_time(e1) / n
     if sustain_s <= 0:
         return ms
+    burst_mhz = None
+    try:
+        probe = GpuClockProbe(torch, ms * n).start()
+        graph.replay()
+        torch.cuda.synchronize()
+        burst_mhz = probe.median_mhz(0.1 * ms * n, 0.9 * ms * n)
+    except Exception:
+        torch.cuda.synchronize()
     reps = max(1, int(sustain_s * 1e3 / max(ms * n, 1e-3)))
     sampler = ClockSampler(gpu_index, period_ms=100).start()
     e0.record()
@@ -285,33 +294,72 @@ def time_rotating(calls, iters, torch, sustain_s=0.0, gpu_index=0):
     e1.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
+    clocks["burst_sm_mhz"] = burst_mhz
     return ms, e0.elapsed_time(e1) / (n * reps), clocks
+
+
+class GpuClockProbe:
+    """The SM clock seen from inside the GPU while a burst of kernels runs: one thread on a side
+    stream records (cycle counter, nanosecond timer) every 20 us (fluke_sm100_clock_samples of
+    lib/libfluke_probe.so). nvidia-smi's samples are 100 ms apart; a dense tcgen05 kernel pulls the
+    clock from its idle maximum down to the power limit's level within a few tens of microseconds,
+    so a burst of a few milliseconds runs at a clock nvidia-smi never shows."""
+    GAP_NS = 20000
+
+    def __init__(self, torch, expected_ms):
+        from fluke_b200 import lib as flib
+        self.torch, self.fn = torch, flib.load_probe().fluke_sm100_clock_samples
+        self.n = int(min(1 << 16, max(64, expected_ms * 1e6 / self.GAP_NS + 64)))
+        self.buf = torch.zeros(2 * self.n, dtype=torch.int64, device="cuda")
+        self.stream = torch.cuda.Stream()
+
+    def start(self):
+        rc = self.fn(self.buf.data_ptr(), self.n, self.GAP_NS, self.stream.cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"fluke_sm100_clock_samples: CUDA error {rc}")
+        return self
+
+    def median_mhz(self, from_ms, to_ms):
+        """Median clock over the samples taken between from_ms and to_ms after the first one."""
+        v = self.buf.cpu().view(self.n, 2).double()
+        t = (v[:, 1] - v[0, 1]) / 1e6
+        mhz = (v[1:, 0] - v[:-1, 0]) / (v[1:, 1] - v[:-1, 1]).clamp_min(1.0) * 1e3
+        sel = (t[1:] >= from_ms) & (t[1:] <= to_ms)
+        return float(mhz[sel].median()) if bool(sel.any()) else None
 
 
 def measure_tensor_peaks(torch):
     """tcgen05.mma issue-rate probe on every SM (operands resident in shared memory, no global
-    traffic): the measured tensor-pipe ceiling for int8 / e4m3 / f16 at the SM clock of the run.
-    MEASURED_PEAKS.json only has bf16 through cuBLAS, so the int8/fp8 fractions of the GEMM-class
-    kernels are quoted against these."""
+    traffic): the measured tensor-pipe ceilings for int8 / e4m3 / f16. MEASURED_PEAKS.json only has
+    bf16 through cuBLAS, so the int8/fp8 fractions of the GEMM-class kernels are quoted against
+    these. Two figures per type: with ZERO operands (nothing toggles, the clock stays at its
+    maximum: the issue rate) and with pseudo-random operands for a few milliseconds (the board's
+    power limit pulls the clock down: what the tensor pipe sustains on real data), each with the SM
+    clock the probe itself measured (cycles / nanoseconds)."""
     from fluke_b200 import lib as flib
     fn = flib.load_probe().fluke_sm100_mma_peak
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-    cyc = torch.zeros(sms, dtype=torch.int64, device="cuda")
+    cyc = torch.zeros(2 * sms, dtype=torch.int64, device="cuda")
     out = {}
-    iters = 16384
     for kind, name, kelems in ((0, "int8", 32), (1, "e4m3", 32), (2, "f16", 16)):
-        fn(kind, 256, iters, cyc.data_ptr(), sms, None)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        rc = fn(kind, 256, iters, cyc.data_ptr(), sms, None)
-        e1.record()
-        torch.cuda.synchronize()
-        if rc != 0:
-            continue
-        ops = 2.0 * 128 * 256 * kelems * iters * sms
-        out[name] = {"TOPs": round(ops / e0.elapsed_time(e1) / 1e9, 1),
-                     "ops_per_clk_per_sm": round(2.0 * 128 * 256 * kelems * iters / cyc.float().mean().item(), 1)}
+        rec = {}
+        for pattern, iters, key in ((0, 16384, ""), (1, 49152, "_random_operands")):
+            fn(kind, 256, iters, pattern, cyc.data_ptr(), sms, None)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fn(kind, 256, iters, pattern, cyc.data_ptr(), sms, None)
+            e1.record()
+            torch.cuda.synchronize()
+            if rc != 0:
+                continue
+            v = cyc.view(sms, 2).double()
+            ops = 2.0 * 128 * 256 * kelems * iters * sms
+            rec["TOPs" + key] = round(ops / e0.elapsed_time(e1) / 1e9, 1)
+            rec["ops_per_clk_per_sm" + key] = round(2.0 * 128 * 256 * kelems * iters / v[:, 0].mean().item(), 1)
+            rec["sm_mhz" + key] = round(float((v[:, 0] / v[:, 1].clamp_min(1.0)).median()) * 1e3, 0)
+        if rec:
+            out[name] = rec
     return out
 
 
@@ -349,6 +397,7 @@ def bench_ops(torch, peaks, tensor_peaks, gpu_index):
     g = torch.Generator().manual_seed(0)
     hbm = peaks["hbm_gbs"]
     cores = host_cores()
+    sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     torch.set_num_threads(cores)
     port.set_threads(cores)
     refcpu = ref.cpu()
@@ -357,15 +406,26 @@ def bench_ops(torch, peaks, tensor_peaks, gpu_index):
     def entry(ms, bytes_, ops_=None, kind=None, sustained=None):
         us = ms * 1e3
         e = {"us": round(us, 2), "GBps": round(bytes_ / ms / 1e6, 1), "frac_hbm": round(bytes_ / ms / 1e6 / hbm, 3)}
+        tp = tensor_peaks.get(kind) or {}
         if ops_:
             e["TOPs"] = round(ops_ / ms / 1e9, 1)
-            peak = (tensor_peaks.get(kind) or {}).get("TOPs")
+            peak = tp.get("TOPs")
             ft, _, ff = roofline_fractions(us, ops_, bytes_, peak, hbm)
             e["frac_tensor"], e["frac_of_floor"], e["tensor_peak_TOPs"] = ft, ff, peak
+            if tp.get("TOPs_random_operands"):
+                # against what the tensor pipe sustains on toggling operands under the power limit
+                e["frac_tensor_powered"] = round(e["TOPs"] / tp["TOPs_random_operands"], 3)
         if sustained and sustained[0] is not None:
             sus_ms, clk = sustained
             e["sustained"] = {"us": round(sus_ms * 1e3, 2), "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons"),
                               "us_x_mhz": round(sus_ms * 1e3 * clk["sm_mhz"], 0) if clk.get("sm_mhz") else None}
+            if clk.get("burst_sm_mhz"):
+                # the timed burst in SM cycles, and (GEMMs) the MMA issue cycles of the same work
+                # on all SMs as a fraction of them: the structural figure, free of the clock
+                cyc = us * clk["burst_sm_mhz"]
+                e["burst"] = {"sm_mhz": round(clk["burst_sm_mhz"], 0), "us_x_mhz": round(cyc, 0)}
+                if ops_ and tp.get("ops_per_clk_per_sm"):
+                    e["burst"]["frac_tensor_cycles"] = round(ops_ / (tp["ops_per_clk_per_sm"] * sm_count) / cyc, 3)
         return e
 
     def cpu(seconds, kind, what):

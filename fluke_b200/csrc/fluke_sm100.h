@@ -63,9 +63,12 @@ int fluke_sm100_fp8_unshuffle(void *dst_nk, const void *src, int N, int K, void 
 
 /* tcgen05.mma issue-rate probe (lib/libfluke_probe.so, not libfluke): n_ctas CTAs each time
  * `iters` back-to-back MMAs of shape 128 x n x 32 bytes (kind 0 int8, 1 e4m3, 2 f16) on
- * shared-memory-resident operands and write their SM-clock cycle counts to cycles_dev[0 .. n_ctas)
- * (device, int64). */
-int fluke_sm100_mma_peak(int kind, int n, int iters, void *cycles_dev, int n_ctas, void *stream);
+ * shared-memory-resident operands (pattern 0: zeros, 1: pseudo-random bytes) and write, per CTA,
+ * their SM-clock cycles and nanoseconds to cycles_dev[0 .. 2 n_ctas) (device, int64). */
+int fluke_sm100_mma_peak(int kind, int n, int iters, int pattern, void *cycles_dev, int n_ctas, void *stream);
+/* Same library: one thread records n pairs (SM cycle counter, nanosecond timer) gap_ns apart into
+ * out_dev (device, int64), so that the clock of kernels running beside it can be read. */
+int fluke_sm100_clock_samples(void *out_dev, int n, int gap_ns, void *stream);
 /* Strided copy between pinned host memory and the device by the copy engine alone (no staging
  * buffer, no kernel): `height` rows of `width` bytes, pitches in bytes. to_device != 0: host ->
  * device, else device -> host. For drivers that place a batch beside another one in a wider

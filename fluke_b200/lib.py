@@ -142,14 +142,17 @@ _PROBE = None
 
 
 def load_probe():
-    """The tcgen05 issue-rate probe the benchmark uses (lib/libfluke_probe.so; not part of libfluke)."""
+    """The tcgen05 issue-rate probe and the in-GPU clock sampler the benchmark uses
+    (lib/libfluke_probe.so; not part of libfluke)."""
     global _PROBE
     if _PROBE is None:
         if not os.path.isfile(PROBE_PATH):
             build()
         _PROBE = ctypes.CDLL(PROBE_PATH)
         _PROBE.fluke_sm100_mma_peak.restype = I
-        _PROBE.fluke_sm100_mma_peak.argtypes = [I, I, I, P, I, P]
+        _PROBE.fluke_sm100_mma_peak.argtypes = [I, I, I, I, P, I, P]
+        _PROBE.fluke_sm100_clock_samples.restype = I
+        _PROBE.fluke_sm100_clock_samples.argtypes = [P, I, I, P]
     return _PROBE
 
 
