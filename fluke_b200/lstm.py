@@ -109,8 +109,8 @@ class StackPipeline:
     and runs each layer once over it (chunks are independent, so the results are those of the
     separate passes). `time_chunks` = C > 1 runs the first and the last layer in C calls over
     consecutive blocks of timesteps, each as soon as its block has been copied in / copied out as
-    soon as it is written. A group is launched when it is full, or earlier when nothing is
-    running, or by `drain()`. Inputs and outputs are pinned host tensors; `submit` only enqueues."""
+    soon as it is written. A group is launched when it is full, or by `drain()`. Inputs and
+    outputs are pinned host tensors; `submit` only enqueues."""
 
     def __init__(self, layers, T, B, device, passes_per_launch=1, time_chunks=1):
         self.layers = layers  # keeps the weight tensors alive
@@ -133,6 +133,12 @@ class StackPipeline:
                                                 1 if zero_state else 0)
         if rc:
             raise RuntimeError(f"fluke_flstm_stream_submit failed: CUDA error {rc}")
+
+    def flush(self):
+        """Launch a group that is only partly filled (without waiting for anything)."""
+        rc = ops._L().fluke_flstm_stream_flush(self._h)
+        if rc:
+            raise RuntimeError(f"fluke_flstm_stream_flush failed: CUDA error {rc}")
 
     def drain(self):
         """Run a group that is only partly filled, then wait until every output has arrived."""

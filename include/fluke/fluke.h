@@ -486,9 +486,9 @@ int fluke_factored_lstm_stack_i8_gpu(
  *            Allocates on the calling thread's current device. NULL on failure.
  *   submit   x_host_i8 [T,B,H], x_scale_host f32 [T*B] and out_host_i8 [T,B,H] are PINNED host
  *            buffers that stay valid until drain. zero_state != 0: the pass starts from c = 0,
- *            h = 0. Only enqueues work. A group is launched when it is full or when nothing is
- *            running.
- *   flush    launches a group that is only partly filled.
+ *            h = 0. Only enqueues work. A group is launched when it is full (P passes).
+ *   flush    launches a group that is only partly filled (a caller whose next pass is not at
+ *            hand yet calls it instead of leaving the GPU idle).
  *   drain    flush, then blocks until every submitted pass's output is in its host buffer.
  *   destroy  waits for outstanding work and frees everything.
  * One host thread per handle. int functions return 0 or a CUDA error code. */

@@ -360,6 +360,27 @@ def test_streaming_pipeline_equals_pass_by_pass(passes_per_launch, time_chunks):
         assert torch.equal(outs[k], ref.cpu())
 
 
+def test_streaming_pipeline_launches_full_groups_and_flush_launches_a_partial_one():
+    """With two passes per launch, `submit` of a lone pass only queues it (its output buffer stays
+    untouched however long one waits); `flush` launches it without blocking, and the bytes are
+    those of the pass alone."""
+    T, B, H, R, NL = 4, 130, 768, 128, 2
+    g = torch.Generator().manual_seed(78)
+    layers = [FactoredLstmLayer.random(H, R, bool(i % 2), g, DEV) for i in range(NL)]
+    pipe = StackPipeline(layers, T, B, DEV, passes_per_launch=2, time_chunks=2)
+    x, xs = prep.quantize_int8_rows(torch.randn(T * B, H, generator=g))
+    x, xs = x.view(T, B, H).contiguous().pin_memory(), xs.contiguous().pin_memory()
+    out = torch.full((T, B, H), 77, dtype=torch.int8).pin_memory()
+    pipe.submit(x, xs, out)
+    torch.cuda.synchronize()
+    assert bool((out == 77).all())          # nothing was launched
+    pipe.flush()
+    pipe.drain()
+    ref, _ = run_stack(layers, x.to(DEV), xs.to(DEV))
+    assert torch.equal(out, ref.cpu())
+    pipe.close()
+
+
 def test_wide_l2_configuration_matches_the_narrow_one(flib):
     """The L2-exchange form with 48 units per gate CTA and one worker per row tile (chosen by itself
     when a layer has more row tiles than a narrow launch holds) computes every element in the same
