@@ -377,3 +377,44 @@ def test_quant_kernel_feeds_the_gemm(be):
     out = ops.qkv_rotary_i8(be, q, w.to(DEV), s, sb.to(DEV), sin.to(DEV), cos.to(DEV), 128)
     exp = port.qkv_rotary_i8(q.cpu().numpy(), w.numpy(), s.cpu().numpy(), sb.numpy(), sin.numpy(), cos.numpy(), 128)
     assert np.array_equal(out.cpu().numpy().view(np.uint16), exp.view(np.uint16))
+
+
+def test_transformer_ops_are_shard_invariant(be, be8):
+    """Replicas-only multi-GPU: a rank takes whole sequences of the token axis and runs the same
+    kernels on its rows. Whatever the split, the concatenated shard outputs are the single-call
+    output bit for bit (no result depends on which tile or CTA a row falls into): RMSNorm+quant,
+    QKV+rotary and the gated MLP, int8 and fp8, 7 sequences of 300 tokens cut 3 + 4 and 1 + 6."""
+    seqlen, n_seq = 300, 7
+    m = seqlen * n_seq
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(m, 512, generator=g).half().to(DEV)
+    w = (torch.randn(512, generator=g) * 0.1 + 1).half().to(DEV)
+    res = torch.randint(-127, 128, (m, 512), generator=g, dtype=torch.int8).to(DEV)
+    rs = (torch.rand(m, generator=g) * 0.02 + 0.001).to(DEV)
+    sin, cos = prep.rotary_tables(seqlen, 64, device=DEV)
+    wq, sq = prep.quantize_int8_rows(torch.randn(1536, 512, generator=g) * 0.02)
+    wg, sg = prep.quantize_int8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    wu, su = prep.quantize_int8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    wq, sq, wg, sg, wu, su = (t.to(DEV) for t in (wq, sq, wg, sg, wu, su))
+    a8, s8 = prep.quantize_fp8_rows(torch.randn(m, 512, generator=g))
+    wq8, sq8 = prep.quantize_fp8_rows(torch.randn(1536, 512, generator=g) * 0.02)
+    wg8, sg8 = prep.quantize_fp8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    wu8, su8 = prep.quantize_fp8_rows(torch.randn(2048, 512, generator=g) * 0.02)
+    a8, s8, wq8, sq8, wg8, sg8, wu8, su8 = (t.to(DEV) for t in (a8, s8, wq8, sq8, wg8, sg8, wu8, su8))
+
+    def run(lo, hi):
+        r, sc = res[lo:hi].clone(), rs[lo:hi].clone()
+        q, qs = ops.rmsnorm_quant_int8(x[lo:hi].contiguous(), w, r, sc, 2.0, 1e-5)
+        qkv = ops.qkv_rotary_i8(be, q, wq, qs, sq, sin, cos, seqlen)
+        mlp = ops.gated_mlp_i8(be, q, wg, wu, qs, sg, su)
+        qkv8 = ops.qkv_rotary_fp8(be8, a8[lo:hi].contiguous(), wq8, s8[lo:hi].contiguous(), sq8, sin, cos, seqlen, plain=True)
+        mlp8 = ops.gated_mlp_fp8(be8, a8[lo:hi].contiguous(), wg8, wu8, s8[lo:hi].contiguous(), sg8, su8, plain=True)
+        torch.cuda.synchronize()
+        return [q, qs, qkv, mlp, qkv8, mlp8]
+
+    whole = run(0, m)
+    for cut in (3, 1):
+        a, b = run(0, cut * seqlen), run(cut * seqlen, m)
+        for full, pa, pb in zip(whole, a, b):
+            assert torch.equal(full, torch.cat([pa, pb], dim=0))
+    assert L.read_status() == 0
