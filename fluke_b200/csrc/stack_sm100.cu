@@ -92,7 +92,6 @@ struct fluke_flstm_stream {
     size_t ws_bytes = 0;
     cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
     long groups = 0;
-    int last_slot = -1;
     struct Pass { const int8_t *x; const float *xs; int8_t *out; };
     std::vector<Pass> pending;
     int zero_state = 1;
@@ -196,7 +195,6 @@ int launch_group(fluke_flstm_stream *s) {
         }
     }
     STACK_TRY(cudaEventRecord(s->ev_out[slot], s->s_out));
-    s->last_slot = slot;
     s->pending.clear();
     return 0;
 }
